@@ -1,0 +1,161 @@
+/*
+ * vkop_cuda.h - C ABI of the CUDA (sm_100a) launcher for vkop's GPU
+ * post-processing operators: Softmax + TopK (fused and unfused) and NMS.
+ *
+ * This is the boundary a vkop build binds instead of its Vulkan dispatch for
+ * these operators.  In the reference an operator's execute() ends in
+ * Operator::submit (ops/Operator.hpp:225-238: descriptor update, pipeline
+ * bind, push constants, vkCmdDispatch) on buffers allocated through VMA
+ * (core/Tensor.hpp:384-394); here execute() ends in one of the calls below on
+ * plain device pointers.
+ *
+ * Conventions for every entry point:
+ *   - all tensor pointers are DEVICE pointers owned by the caller; tensors are
+ *     the logical row-major arrays ([rows, cols] logits, boxes [B,N,4],
+ *     scores [B,C,N]), not the RGBA image packing the shaders read;
+ *   - the call enqueues work on `stream` (a cudaStream_t passed as void*; NULL
+ *     is the default stream) and returns without synchronising;
+ *   - nothing is allocated; scratch memory comes from the caller
+ *     (`*_workspace` tells how much).  A workspace must be cleared once with
+ *     vkop_cuda_workspace_init after it is allocated; kernels leave it ready
+ *     for the next call.  One workspace serves one call in flight at a time;
+ *   - the return value is VKOP_OK (0) or a negative vkop_status; the library
+ *     never throws and never aborts.
+ */
+#ifndef VKOP_CUDA_H_
+#define VKOP_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VKOP_CUDA_VERSION 100
+
+typedef enum vkop_status {
+    VKOP_OK = 0,
+    VKOP_INVALID_ARG = -1,
+    VKOP_UNSUPPORTED = -2,
+    VKOP_WORKSPACE_TOO_SMALL = -3,
+    VKOP_CUDA_ERROR = -4,
+    VKOP_TIMEOUT = -5
+} vkop_status;
+
+typedef enum vkop_dtype { VKOP_F32 = 0, VKOP_F16 = 1, VKOP_BF16 = 2 } vkop_dtype;
+typedef enum vkop_index_dtype { VKOP_I32 = 0, VKOP_I64 = 1 } vkop_index_dtype;
+typedef enum vkop_value_kind { VKOP_VALUE_PROBABILITY = 0, VKOP_VALUE_RAW = 1 } vkop_value_kind;
+typedef enum vkop_select_path { VKOP_PATH_AUTO = 0, VKOP_PATH_CHUNK = 1, VKOP_PATH_RADIX = 2 } vkop_select_path;
+
+/* Library version (VKOP_CUDA_VERSION of the build). */
+int vkop_cuda_version(void);
+/* Static, human-readable name of a status code. */
+const char *vkop_cuda_status_string(int status);
+/* Kernels launched by this library in the calling process so far. */
+uint64_t vkop_cuda_launch_count(void);
+
+/* Clears a freshly allocated workspace (asynchronous on `stream`). */
+int vkop_cuda_workspace_init(void *workspace, size_t bytes, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Fused Softmax + TopK over the last axis of a [rows, cols] tensor.
+ *
+ * Replaces the Softmax dispatch followed by the multi-pass TopK dispatches of
+ * the reference (ops/Softmax.hpp:61-141 with shaders/softmax2.comp:50-117;
+ * ops/Topk.hpp:95-217 with shaders/topk.comp:110-175) as registered by
+ * benchmark/main.cpp:85-101 through Runtime::RegisterPostProcess
+ * (core/runtime.cpp:480-520).
+ *
+ * Selection is on the stored logit: value descending, lower index first among
+ * equal values (-0 equals +0, NaN ranks above +inf).  Output values are the
+ * softmax probabilities of x * inv_temperature (or the raw logits), in the
+ * logits' dtype; indices are int32 (as the reference) or int64 (ONNX).
+ * Outputs are [rows, k], row-major, sorted best first. */
+typedef struct vkop_softmax_topk_desc {
+    int64_t rows;
+    int64_t cols;
+    int64_t row_stride;    /* elements between rows of the logits; 0 means cols */
+    int32_t dtype;         /* vkop_dtype of logits and of the output values */
+    int32_t k;             /* 1 <= k <= min(cols, 4096) */
+    int32_t index_dtype;   /* vkop_index_dtype */
+    int32_t value_kind;    /* vkop_value_kind */
+    float inv_temperature; /* > 0; 1.0f for a plain softmax */
+    int32_t largest;       /* 1 = largest (default semantic); 0 = smallest, raw values only */
+    int32_t path;          /* vkop_select_path; AUTO picks by k and row length */
+    int32_t splits;        /* CTAs per row on the chunk path; 0 = automatic */
+    int64_t index_offset;  /* added to every emitted index (offset of a vocabulary shard) */
+} vkop_softmax_topk_desc;
+
+int vkop_cuda_softmax_topk_workspace(const vkop_softmax_topk_desc *desc, size_t *bytes);
+int vkop_cuda_softmax_topk(const vkop_softmax_topk_desc *desc, const void *logits, void *out_values,
+                           void *out_indices, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Standalone TopK (no softmax): same selection, values are copies of the
+ * input.  Replaces ops/Topk.hpp:95-217 + shaders/topk.comp when TopK is used
+ * on its own (tests/TopkTest.cpp:91-125).  desc->value_kind is ignored. */
+int vkop_cuda_topk(const vkop_softmax_topk_desc *desc, const void *input, void *out_values, void *out_indices,
+                   void *workspace, size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Unfused Softmax with the full probability tensor as output, along the
+ * middle axis of a row-major [outer, axis_len, inner] view (inner = 1 for the
+ * 2-D post-processing case).  Replaces ops/Softmax.hpp:61-141 with
+ * shaders/softmax2.comp (rank <= 2) and shaders/softmax.comp (rank 3/4, whose
+ * image packing is not reproduced: the tensor stays linear NCHW). */
+typedef struct vkop_softmax_desc {
+    int64_t outer;
+    int64_t axis_len;
+    int64_t inner;
+    int32_t dtype; /* input and output dtype */
+    float inv_temperature;
+} vkop_softmax_desc;
+
+int vkop_cuda_softmax(const vkop_softmax_desc *desc, const void *input, void *output, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Vocabulary-sharded Softmax + TopK.  Each GPU holds [rows, cols] = one
+ * contiguous column slice of the logits (desc->index_offset = first global
+ * column).  `partial` writes one packet per row: the shard's softmax maximum
+ * and exp-sum and its k best (key, global index) pairs.  The packets of all
+ * shards are exchanged by the caller (an all-gather), and `merge` reduces
+ * `shards` packets per row to the final [rows, k] outputs.  The reference has
+ * no multi-device path; this extends the operator above. */
+size_t vkop_cuda_packet_bytes(int32_t k);
+int vkop_cuda_softmax_topk_partial(const vkop_softmax_topk_desc *desc, const void *logits_shard, void *packets_out,
+                                   void *workspace, size_t workspace_bytes, void *stream);
+/* packets: [shards, rows, packet] as an all-gather of packets_out delivers them. */
+int vkop_cuda_softmax_topk_merge(const vkop_softmax_topk_desc *desc, const void *packets, int32_t shards,
+                                 void *out_values, void *out_indices, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* NMS (ONNX NonMaxSuppression) per (batch, class).
+ *
+ * Replaces ops/Nms.hpp:66-112 with shaders/nms.comp:70-203.  boxes [B,N,4]
+ * fp32, scores [B,C,N] fp32.  Candidates are boxes with score >
+ * score_threshold, ordered by score descending then index ascending; with
+ * pre_topk > 0 only the best pre_topk of them enter the sweep.  IoU is
+ * computed in fp32 in the shader's operand order (nms.comp:57-68).  Output
+ * rows are (batch, class, box) int32 triples in (batch, class, rank) order;
+ * *out_count receives the number of rows produced (rows beyond
+ * capacity_rows are counted but not written). */
+typedef struct vkop_nms_desc {
+    int32_t num_batch;
+    int32_t num_class;
+    int32_t num_boxes;
+    int32_t center_point_box;           /* 0: (x1,y1,x2,y2); 1: (cx,cy,w,h) */
+    int32_t max_output_boxes_per_class; /* 0 = unlimited */
+    int32_t pre_topk;                   /* 0 = every candidate enters the sweep */
+    float iou_threshold;
+    float score_threshold;
+    int64_t capacity_rows;              /* rows out_rows can hold */
+} vkop_nms_desc;
+
+int vkop_cuda_nms_workspace(const vkop_nms_desc *desc, size_t *bytes);
+int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scores, int32_t *out_rows,
+                  int32_t *out_count, void *workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VKOP_CUDA_H_ */

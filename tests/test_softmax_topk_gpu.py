@@ -1,0 +1,214 @@
+"""GPU parity of the fused Softmax + TopK (C ABI) against the CPU oracle."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests import util
+from vkop_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from vkop_b200 import capi as c
+
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return c
+
+
+def test_reference_topk_cases(capi):
+    """tests/TopkTest.cpp cases (seed 56): standalone TopK on the stored inputs, against the stored torch outputs."""
+    g = np.load(os.path.join(GOLDEN, "topk_seed56.npz"))
+    for n in range(5):
+        k = int(g[f"case{n}_k"])
+        x = torch.from_numpy(g[f"case{n}_f32_input"])
+        v, i = capi.softmax_topk(x.cuda(), k, standalone_topk=True)
+        assert np.array_equal(i.cpu().numpy(), g[f"case{n}_f32_indices"])
+        assert np.array_equal(v.cpu().numpy(), g[f"case{n}_f32_values"])
+        xh = torch.from_numpy(g[f"case{n}_f16_input"].view(np.float16))
+        v, i = capi.softmax_topk(xh.cuda(), k, standalone_topk=True)
+        # fp16 random data holds equal values; torch.topk's tie order is not canonical -> compare values bit-exactly
+        # and indices with the oracle
+        assert np.array_equal(v.cpu().numpy().view(np.uint16), g[f"case{n}_f16_values"])
+        _, wi = oracle.topk(g[f"case{n}_f16_input"], k, dtype=oracle.F16)
+        assert np.array_equal(i.cpu().numpy(), wi)
+
+
+def test_classifier_head(capi):
+    x = workloads.classifier_head()
+    util.check_fused(x, 5, what="C1")
+
+
+def test_batched_classifier_ties_int64(capi):
+    x = workloads.batched_classifier()
+    vals, idx = util.check_fused(x, 5, what="C2", index_dtype=capi.I64)
+    assert idx.dtype == torch.int64
+    # the quantised rows do hold ties inside the top 5 somewhere; the canonical order is (value desc, index asc)
+    st = torch.sort(x, dim=1, stable=True, descending=True)[1][:, :5]
+    assert torch.equal(idx.cpu(), st)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_llm_vocab(capi, dtype):
+    x = workloads.llm_vocab(dtype=dtype)
+    util.check_fused(x, workloads.LLM_K, workloads.LLM_INV_TEMPERATURE, what=f"C3 {dtype}")
+
+
+def test_llm_vocab_deterministic(capi):
+    x = workloads.llm_vocab().cuda()
+    a = capi.softmax_topk(x, 50, 1.25)
+    b = capi.softmax_topk(x, 50, 1.25)
+    torch.cuda.synchronize()
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_sharded_vocab_shape_single_gpu(capi):
+    x = workloads.sharded_vocab(rows=32)
+    util.check_fused(x, 64, what="C5 rows[0:32] on one GPU")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_small_exhaustive(capi, dtype):
+    """Every n in 1..70 and every k in 1..n, on rows holding ties, signed zeros and infinities."""
+    g = torch.Generator().manual_seed(11)
+    for n in range(1, 71):
+        x = torch.randn(6, n, generator=g)
+        x[1] = torch.round(x[1] * 2) / 2          # heavy ties
+        x[2] = 0.0
+        x[2, ::2] = -0.0                          # signed zeros only
+        x[3, ::3] = float("-inf")
+        x[4] = 1.5                                # all equal
+        if n > 2:
+            x[5, 1] = float("inf") if n % 2 else 3.0
+        x = x.to(dtype)
+        for k in range(1, n + 1):
+            if k > 128:
+                break
+            util.check_fused(x, k, what=f"n={n} k={k} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unaligned_rows(capi, dtype):
+    """Row starts that are not 16-byte aligned (odd strides, offset base pointers)."""
+    g = torch.Generator().manual_seed(12)
+    for cols, stride, off in [(1000, 1001, 1), (777, 779, 3), (4099, 4101, 5), (20000, 20003, 2)]:
+        buf = torch.randn(8 * stride + 16, generator=g).to(dtype)
+        x_cpu = buf[off:off + 8 * stride].view(8, stride)[:, :cols]
+        bg = buf.cuda()
+        xg = bg[off:off + 8 * stride].view(8, stride)[:, :cols]
+        vals, idx = capi.softmax_topk(xg, 9)
+        wv, wi = util.oracle_softmax_topk(x_cpu.contiguous(), 9)
+        util.assert_indices_equal(idx, wi, f"unaligned cols={cols}")
+        util.assert_probs_close(vals, wv, dtype, f"unaligned cols={cols}")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 8, 16, 33])
+def test_forced_splits(capi, splits):
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(5, 16000, generator=g)
+    x[0, :4000] = x[0, 4000:8000]  # duplicated values across chunks -> ties across packets
+    util.check_fused(x, 50, 1.25, what=f"splits={splits}", splits=splits)
+
+
+def test_few_rows_many_chunks(capi):
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(1, 300000, generator=g)
+    util.check_fused(x, 64, what="1 x 300000")
+    x = torch.randn(3, 1000003, generator=g).to(torch.bfloat16)
+    util.check_fused(x, 17, what="3 x 1000003 bf16")
+
+
+def test_fallback_paths(capi):
+    """Inputs that defeat the threshold filter: all-equal rows, massive ties, NaN."""
+    x = torch.zeros(4, 40000)
+    x[1] = 2.0
+    x[2, 777] = 3.0
+    x[3] = torch.arange(40000) % 7
+    util.check_fused(x, 50, what="all-equal / massive ties")
+    for dt in (torch.float16, torch.bfloat16):
+        util.check_fused(x.to(dt), 50, what=f"massive ties {dt}")
+    # NaN ranks above +inf (torch ordering); the probabilities of such a row are NaN
+    y = torch.randn(2, 5000, generator=torch.Generator().manual_seed(15))
+    y[0, 1234] = float("nan")
+    y[0, 99] = float("nan")
+    y[1, 7] = float("inf")
+    vals, idx = capi.softmax_topk(y.cuda(), 5)
+    wv, wi = util.oracle_softmax_topk(y, 5)
+    util.assert_indices_equal(idx, wi, "NaN rows")
+    assert idx[0, 0].item() == 99 and idx[0, 1].item() == 1234
+    assert torch.isnan(vals[0]).all()
+
+
+def test_raw_value_kind_and_smallest(capi):
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(7, 3000, generator=g)
+    x[0, 5] = -0.0
+    x[0, 6] = 0.0
+    xg = x.cuda()
+    v, i = capi.softmax_topk(xg, 11, value_kind=capi.VALUE_RAW)
+    wv, wi = oracle.topk(x.numpy(), 11)
+    assert np.array_equal(i.cpu().numpy(), wi) and np.array_equal(v.cpu().numpy().view(np.uint32), wv.view(np.uint32))
+    v, i = capi.softmax_topk(xg, 11, standalone_topk=True, largest=False)
+    wv, wi = oracle.topk(x.numpy(), 11, largest=False)
+    assert np.array_equal(i.cpu().numpy(), wi) and np.array_equal(v.cpu().numpy().view(np.uint32), wv.view(np.uint32))
+
+
+def test_index_offset(capi):
+    x = torch.randn(3, 2000, generator=torch.Generator().manual_seed(17))
+    _, i0 = capi.softmax_topk(x.cuda(), 8)
+    _, i1 = capi.softmax_topk(x.cuda(), 8, index_offset=123456, index_dtype=capi.I64)
+    assert torch.equal(i0.long() + 123456, i1)
+
+
+def test_partial_and_merge_single_device(capi):
+    """Vocabulary sharding emulated on one GPU: packets of G column slices, merged."""
+    x = workloads.sharded_vocab(rows=16, cols=64000)
+    xg = x.cuda()
+    k = 64
+    for G in (1, 2, 4, 8):
+        w = x.shape[1] // G
+        packets = torch.stack([capi.softmax_topk_partial(xg[:, g * w:(g + 1) * w], k, g * w) for g in range(G)])
+        vals, idx = capi.softmax_topk_merge(packets, x.shape[0], k, x.dtype)
+        wv, wi = util.oracle_softmax_topk(x, k)
+        util.assert_indices_equal(idx, wi, f"G={G}")
+        util.assert_probs_close(vals, wv, x.dtype, f"G={G}")
+
+
+def test_argument_errors(capi):
+    x = torch.randn(2, 100).cuda()
+    with pytest.raises(capi.VkopError) as e:
+        capi.softmax_topk(x, 101)
+    assert e.value.status == capi.INVALID_ARG
+    with pytest.raises(capi.VkopError):
+        capi.softmax_topk(x, 0)
+    with pytest.raises(capi.VkopError):
+        capi.softmax_topk(x, 5, inv_temperature=0.0)
+    with pytest.raises(capi.VkopError):
+        capi.softmax_topk(x, 5, inv_temperature=float("nan"))
+    d = capi.make_desc(x, 5)
+    import ctypes as C
+    L = capi.lib()
+    assert L.vkop_cuda_softmax_topk(C.byref(d), None, None, None, None, 0, None) == capi.INVALID_ARG
+    assert L.vkop_cuda_softmax_topk(None, None, None, None, None, 0, None) == capi.INVALID_ARG
+    # too small a workspace for a multi-chunk plan
+    y = torch.randn(4, 200000).cuda()
+    d = capi.make_desc(y, 50)
+    need = capi.softmax_topk_workspace_bytes(d)
+    assert need > 0
+    v = torch.empty(4, 50).cuda()
+    i = torch.empty(4, 50, dtype=torch.int32).cuda()
+    small = torch.empty(16, dtype=torch.uint8).cuda()
+    rc = L.vkop_cuda_softmax_topk(C.byref(d), y.data_ptr(), v.data_ptr(), i.data_ptr(), small.data_ptr(), 16, None)
+    assert rc == capi.WORKSPACE_TOO_SMALL
+    # zero rows is a valid no-op
+    z = torch.empty(0, 100).cuda()
+    capi.softmax_topk(z, 5)

@@ -1,0 +1,215 @@
+// C ABI: argument validation and dispatch.  Declared in include/vkop_cuda.h.
+#include <atomic>
+#include <cmath>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace vkop_cuda {
+
+static std::atomic<uint64_t> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+static int validate_select(const vkop_softmax_topk_desc *d, bool check_ptrs, const void *in, bool need_outputs,
+                           const void *ov, const void *oi) {
+    if (!d)
+        return VKOP_INVALID_ARG;
+    if (d->rows < 0 || d->cols < 1 || d->k < 1 || d->k > d->cols || d->k > kMaxK)
+        return VKOP_INVALID_ARG;
+    if (d->dtype != VKOP_F32 && d->dtype != VKOP_F16 && d->dtype != VKOP_BF16)
+        return VKOP_INVALID_ARG;
+    if (d->index_dtype != VKOP_I32 && d->index_dtype != VKOP_I64)
+        return VKOP_INVALID_ARG;
+    if (d->value_kind != VKOP_VALUE_PROBABILITY && d->value_kind != VKOP_VALUE_RAW)
+        return VKOP_INVALID_ARG;
+    if (!(d->inv_temperature > 0.0f) || !std::isfinite(d->inv_temperature))
+        return VKOP_INVALID_ARG;
+    if (d->row_stride != 0 && d->row_stride < d->cols)
+        return VKOP_INVALID_ARG;
+    if (d->path < VKOP_PATH_AUTO || d->path > VKOP_PATH_RADIX || d->splits < 0)
+        return VKOP_INVALID_ARG;
+    if (d->index_offset < 0 || d->index_offset + d->cols > 0xFFFFFFFFll)
+        return VKOP_INVALID_ARG;
+    if (d->index_dtype == VKOP_I32 && d->index_offset + d->cols > 0x7FFFFFFFll)
+        return VKOP_INVALID_ARG;
+    if (check_ptrs && d->rows > 0) {
+        if (!in || (need_outputs && (!ov || !oi)))
+            return VKOP_INVALID_ARG;
+        const size_t esz = d->dtype == VKOP_F32 ? 4 : 2;
+        if (reinterpret_cast<uintptr_t>(in) % esz != 0)
+            return VKOP_INVALID_ARG;
+    }
+    return VKOP_OK;
+}
+
+// Chooses the path and sizes the scratch memory.
+static int plan_select(const vkop_softmax_topk_desc &d, SelectPlan *plan) {
+    plan->use_radix = false;
+    int rc = VKOP_UNSUPPORTED;
+    if (d.path != VKOP_PATH_RADIX)
+        rc = plan_chunk(d, &plan->chunk);
+    if (rc == VKOP_OK) {
+        plan->bytes = plan->chunk.counters_bytes + plan->chunk.packets_bytes;
+        return VKOP_OK;
+    }
+    if (d.path == VKOP_PATH_CHUNK)
+        return rc;
+    plan->use_radix = true;
+    rc = plan_radix(d, &plan->radix);
+    if (rc == VKOP_OK)
+        plan->bytes = plan->radix.bytes;
+    return rc;
+}
+
+static int run_select(const vkop_softmax_topk_desc &d, const void *in, void *ov, void *oi, void *packets_out,
+                      void *ws, size_t ws_bytes, int need_sum, void *stream) {
+    SelectPlan plan;
+    int rc = plan_select(d, &plan);
+    if (rc != VKOP_OK)
+        return rc;
+    if (plan.bytes > 0 && (!ws || ws_bytes < plan.bytes))
+        return VKOP_WORKSPACE_TOO_SMALL;
+    if (plan.bytes > 0 && reinterpret_cast<uintptr_t>(ws) % 16 != 0)
+        return VKOP_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (plan.use_radix)
+        return launch_radix(d, plan.radix, in, ov, oi, packets_out, ws, need_sum, s);
+    return launch_chunk(d, plan.chunk, in, ov, oi, packets_out, ws, need_sum, s);
+}
+
+}  // namespace vkop_cuda
+
+using namespace vkop_cuda;
+
+extern "C" {
+
+int vkop_cuda_version(void) { return VKOP_CUDA_VERSION; }
+
+const char *vkop_cuda_status_string(int status) {
+    switch (status) {
+    case VKOP_OK: return "VKOP_OK";
+    case VKOP_INVALID_ARG: return "VKOP_INVALID_ARG";
+    case VKOP_UNSUPPORTED: return "VKOP_UNSUPPORTED";
+    case VKOP_WORKSPACE_TOO_SMALL: return "VKOP_WORKSPACE_TOO_SMALL";
+    case VKOP_CUDA_ERROR: return "VKOP_CUDA_ERROR";
+    case VKOP_TIMEOUT: return "VKOP_TIMEOUT";
+    default: return "VKOP_UNKNOWN_STATUS";
+    }
+}
+
+uint64_t vkop_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int vkop_cuda_workspace_init(void *workspace, size_t bytes, void *stream) {
+    if (bytes == 0)
+        return VKOP_OK;
+    if (!workspace)
+        return VKOP_INVALID_ARG;
+    return cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream)) == cudaSuccess ? VKOP_OK
+                                                                                                   : VKOP_CUDA_ERROR;
+}
+
+int vkop_cuda_softmax_topk_workspace(const vkop_softmax_topk_desc *desc, size_t *bytes) {
+    if (!bytes)
+        return VKOP_INVALID_ARG;
+    int rc = validate_select(desc, false, nullptr, false, nullptr, nullptr);
+    if (rc != VKOP_OK)
+        return rc;
+    SelectPlan plan;
+    rc = plan_select(*desc, &plan);
+    if (rc != VKOP_OK)
+        return rc;
+    *bytes = plan.bytes;
+    return VKOP_OK;
+}
+
+int vkop_cuda_softmax_topk(const vkop_softmax_topk_desc *desc, const void *logits, void *out_values,
+                           void *out_indices, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = validate_select(desc, true, logits, true, out_values, out_indices);
+    if (rc != VKOP_OK)
+        return rc;
+    if (!desc->largest && desc->value_kind != VKOP_VALUE_RAW)
+        return VKOP_UNSUPPORTED;  // "smallest" is a TopK attribute; softmax of the smallest is not a reference path
+    return run_select(*desc, logits, out_values, out_indices, nullptr, workspace, workspace_bytes,
+                      desc->value_kind == VKOP_VALUE_PROBABILITY, stream);
+}
+
+int vkop_cuda_topk(const vkop_softmax_topk_desc *desc, const void *input, void *out_values, void *out_indices,
+                   void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = validate_select(desc, true, input, true, out_values, out_indices);
+    if (rc != VKOP_OK)
+        return rc;
+    vkop_softmax_topk_desc d = *desc;
+    d.value_kind = VKOP_VALUE_RAW;
+    return run_select(d, input, out_values, out_indices, nullptr, workspace, workspace_bytes, 0, stream);
+}
+
+size_t vkop_cuda_packet_bytes(int32_t k) { return k > 0 ? static_cast<size_t>(packet_words(k)) * 4 : 0; }
+
+int vkop_cuda_softmax_topk_partial(const vkop_softmax_topk_desc *desc, const void *logits_shard, void *packets_out,
+                                   void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = validate_select(desc, true, logits_shard, false, nullptr, nullptr);
+    if (rc != VKOP_OK)
+        return rc;
+    if (desc->rows > 0 && !packets_out)
+        return VKOP_INVALID_ARG;
+    if (!desc->largest)
+        return VKOP_UNSUPPORTED;
+    vkop_softmax_topk_desc d = *desc;
+    d.value_kind = VKOP_VALUE_PROBABILITY;
+    return run_select(d, logits_shard, nullptr, nullptr, packets_out, workspace, workspace_bytes, 1, stream);
+}
+
+int vkop_cuda_softmax_topk_merge(const vkop_softmax_topk_desc *desc, const void *packets, int32_t shards,
+                                 void *out_values, void *out_indices, void *stream) {
+    if (!desc || shards < 1)
+        return VKOP_INVALID_ARG;
+    if (desc->rows < 0 || desc->k < 1 || desc->k > kMaxK)
+        return VKOP_INVALID_ARG;
+    if (desc->dtype != VKOP_F32 && desc->dtype != VKOP_F16 && desc->dtype != VKOP_BF16)
+        return VKOP_INVALID_ARG;
+    if (desc->index_dtype != VKOP_I32 && desc->index_dtype != VKOP_I64)
+        return VKOP_INVALID_ARG;
+    if (!(desc->inv_temperature > 0.0f) || !std::isfinite(desc->inv_temperature))
+        return VKOP_INVALID_ARG;
+    if (desc->rows > 0 && (!packets || !out_values || !out_indices))
+        return VKOP_INVALID_ARG;
+    return launch_merge(*desc, packets, shards, out_values, out_indices, static_cast<cudaStream_t>(stream));
+}
+
+int vkop_cuda_softmax(const vkop_softmax_desc *desc, const void *input, void *output, void *stream) {
+    if (!desc || desc->outer < 0 || desc->axis_len < 1 || desc->inner < 1)
+        return VKOP_INVALID_ARG;
+    if (desc->dtype != VKOP_F32 && desc->dtype != VKOP_F16 && desc->dtype != VKOP_BF16)
+        return VKOP_INVALID_ARG;
+    if (!(desc->inv_temperature > 0.0f) || !std::isfinite(desc->inv_temperature))
+        return VKOP_INVALID_ARG;
+    if (desc->outer > 0 && (!input || !output))
+        return VKOP_INVALID_ARG;
+    return launch_softmax(*desc, input, output, static_cast<cudaStream_t>(stream));
+}
+
+int vkop_cuda_nms_workspace(const vkop_nms_desc *desc, size_t *bytes) {
+    if (!desc || !bytes)
+        return VKOP_INVALID_ARG;
+    return plan_nms(*desc, bytes);
+}
+
+int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scores, int32_t *out_rows,
+                  int32_t *out_count, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!desc || !out_count)
+        return VKOP_INVALID_ARG;
+    size_t need = 0;
+    int rc = plan_nms(*desc, &need);
+    if (rc != VKOP_OK)
+        return rc;
+    const int64_t problems = static_cast<int64_t>(desc->num_batch) * desc->num_class;
+    if (problems > 0 && desc->num_boxes > 0 && (!boxes || !scores))
+        return VKOP_INVALID_ARG;
+    if (desc->capacity_rows > 0 && !out_rows)
+        return VKOP_INVALID_ARG;
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return VKOP_WORKSPACE_TOO_SMALL;
+    return launch_nms(*desc, boxes, scores, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

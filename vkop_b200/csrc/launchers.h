@@ -1,0 +1,51 @@
+// Internal interface between the C ABI (capi.cu) and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "vkop_cuda.h"
+
+namespace vkop_cuda {
+
+constexpr int kMaxK = 4096;  // largest k any path serves
+
+// ---- chunk path (softmax_topk.cu) ----
+struct ChunkPlan {
+    int cfg;
+    int splits;
+    int64_t vps;
+    size_t counters_bytes, packets_bytes, smem_bytes;
+};
+int plan_chunk(const vkop_softmax_topk_desc &d, ChunkPlan *plan);
+int launch_chunk(const vkop_softmax_topk_desc &d, const ChunkPlan &plan, const void *logits, void *out_values,
+                 void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream);
+int launch_merge(const vkop_softmax_topk_desc &d, const void *packets, int shards, void *out_values,
+                 void *out_indices, cudaStream_t stream);
+
+// ---- radix path (radix_select.cu) ----
+struct RadixPlan {
+    size_t bytes;
+    int ctas_per_row;
+};
+int plan_radix(const vkop_softmax_topk_desc &d, RadixPlan *plan);
+int launch_radix(const vkop_softmax_topk_desc &d, const RadixPlan &plan, const void *logits, void *out_values,
+                 void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream);
+
+struct SelectPlan {
+    bool use_radix;
+    ChunkPlan chunk;
+    RadixPlan radix;
+    size_t bytes;
+};
+
+// ---- unfused softmax (softmax.cu) ----
+int launch_softmax(const vkop_softmax_desc &d, const void *input, void *output, cudaStream_t stream);
+
+// ---- NMS (nms.cu) ----
+int plan_nms(const vkop_nms_desc &d, size_t *bytes);
+int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, int32_t *out_rows, int32_t *out_count,
+               void *workspace, cudaStream_t stream);
+
+}  // namespace vkop_cuda
