@@ -16,6 +16,7 @@ struct ChunkPlan {
     int cfg;
     int splits;
     int64_t vps;
+    int list_cap;  // candidates one chunk may publish when a row has several chunks
     size_t counters_bytes, packets_bytes, smem_bytes;
 };
 int plan_chunk(const vkop_softmax_topk_desc &d, ChunkPlan *plan);
