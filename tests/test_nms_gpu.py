@@ -1,0 +1,126 @@
+"""GPU parity of NMS (C ABI) against the CPU oracle and the stored reference-test expectations."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from vkop_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from vkop_b200 import capi as c
+
+    assert torch.cuda.is_available()
+    return c
+
+
+def run_both(capi, boxes, scores, **kw):
+    rows, count = capi.nms(boxes.cuda(), scores.cuda(), **kw)
+    torch.cuda.synchronize()
+    n = int(count.item())
+    want_rows, want_total, _ = oracle.nms(boxes.numpy(), scores.numpy(), **kw)
+    assert n == want_total, (n, want_total)
+    got = rows[:min(n, rows.shape[0])].cpu().numpy()
+    assert np.array_equal(got, want_rows[:got.shape[0]])
+    return got
+
+
+def test_reference_nms_cases(capi):
+    """tests/NmsTest.cpp:181-185 shapes and thresholds; expectation = the test's own greedy NMS (stored)."""
+    g = np.load(os.path.join(GOLDEN, "nms_cases.npz"))
+    for n in range(3):
+        boxes, scores = torch.from_numpy(g[f"case{n}_boxes"]), torch.from_numpy(g[f"case{n}_scores"])
+        max_per_class, iou_thr, score_thr = g[f"case{n}_params"]
+        got = run_both(capi, boxes, scores, iou_threshold=float(iou_thr), score_threshold=float(score_thr))
+        assert np.array_equal(got, g[f"case{n}_expected"])
+        if max_per_class > 0:
+            run_both(capi, boxes, scores, iou_threshold=float(iou_thr), score_threshold=float(score_thr),
+                     max_output_boxes_per_class=int(max_per_class))
+
+
+def test_yolo_detect_subset(capi):
+    boxes, scores = workloads.yolo_detect(batch=2, classes=12)
+    got = run_both(capi, boxes, scores, **workloads.YOLO_PARAMS)
+    assert got.shape[0] > 0
+
+
+def test_yolo_detect_full(capi):
+    boxes, scores = workloads.yolo_detect()
+    run_both(capi, boxes, scores, **workloads.YOLO_PARAMS)
+
+
+def test_small_and_edge(capi):
+    g = torch.Generator().manual_seed(41)
+    for B, C, N in [(1, 1, 1), (2, 3, 5), (1, 2, 33), (3, 1, 257), (1, 1, 1000)]:
+        xy = torch.rand(B, N, 2, generator=g) * 10
+        wh = torch.rand(B, N, 2, generator=g) * 4 + 0.1
+        boxes = torch.cat([xy, xy + wh], -1)
+        scores = torch.rand(B, C, N, generator=g)
+        scores[..., ::5] = scores[..., 1::5][..., :scores[..., ::5].shape[-1]] if N > 5 else scores[..., ::5]  # tied scores
+        for kw in [dict(iou_threshold=0.5, score_threshold=0.1),
+                   dict(iou_threshold=0.0, score_threshold=0.0),
+                   dict(iou_threshold=0.3, score_threshold=0.5, max_output_boxes_per_class=3),
+                   dict(iou_threshold=0.45, score_threshold=0.2, pre_topk=7, max_output_boxes_per_class=5),
+                   dict(iou_threshold=1.0, score_threshold=0.0),
+                   dict(iou_threshold=0.5, score_threshold=2.0)]:
+            run_both(capi, boxes, scores, **kw)
+
+
+def test_center_point_and_degenerate_boxes(capi):
+    g = torch.Generator().manual_seed(42)
+    N = 400
+    boxes = torch.cat([torch.rand(1, N, 2, generator=g) * 50, torch.rand(1, N, 2, generator=g) * 20], -1)
+    boxes[0, ::7, 2:] = 0.0          # zero-area boxes
+    boxes[0, 5] = boxes[0, 6]        # identical boxes
+    scores = torch.rand(1, 4, N, generator=g)
+    scores[0, :, 5] = scores[0, :, 6]
+    run_both(capi, boxes, scores, center_point_box=1, iou_threshold=0.4, score_threshold=0.05)
+
+
+def test_large_candidate_sets(capi):
+    """Problems beyond the bit-mask sweep (iterative sweep) and beyond the sort buffer (radix pre-selection)."""
+    g = torch.Generator().manual_seed(43)
+    N = 3000
+    xy = torch.rand(1, N, 2, generator=g) * 300
+    wh = torch.rand(1, N, 2, generator=g) * 30 + 1
+    boxes = torch.cat([xy, xy + wh], -1)
+    scores = torch.rand(1, 2, N, generator=g)
+    run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05)          # ~2850 candidates, no pre-selection
+    run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05, pre_topk=200)  # overflow of the 1024 sort buffer
+    run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05, pre_topk=1500, max_output_boxes_per_class=100)
+
+
+def test_capacity_and_repeat(capi):
+    boxes, scores = workloads.yolo_detect(batch=1, classes=4)
+    kw = dict(workloads.YOLO_PARAMS)
+    rows, count = capi.nms(boxes.cuda(), scores.cuda(), capacity_rows=10, **kw)
+    want_rows, total, _ = oracle.nms(boxes.numpy(), scores.numpy(), **kw)
+    assert int(count.item()) == total and total > 10
+    assert np.array_equal(rows[:10].cpu().numpy(), want_rows[:10])
+    # the same workspace serves consecutive calls
+    d = capi.NmsDesc(num_batch=1, num_class=4, num_boxes=8400, center_point_box=1, max_output_boxes_per_class=300,
+                     pre_topk=300, iou_threshold=0.45, score_threshold=0.25, capacity_rows=1200)
+    ws = capi.Workspace(capi.nms_workspace_bytes(d))
+    a = capi.nms(boxes.cuda(), scores.cuda(), workspace=ws, **kw)
+    b = capi.nms(boxes.cuda(), scores.cuda(), workspace=ws, **kw)
+    assert torch.equal(a[0][:total], b[0][:total]) and int(b[1].item()) == total
+
+
+def test_argument_errors(capi):
+    import ctypes as C
+    L = capi.lib()
+    d = capi.NmsDesc(num_batch=1, num_class=1, num_boxes=10000, center_point_box=0, max_output_boxes_per_class=0,
+                     pre_topk=0, iou_threshold=0.5, score_threshold=0.1, capacity_rows=10)
+    n = C.c_size_t()
+    assert L.vkop_cuda_nms_workspace(C.byref(d), C.byref(n)) == capi.UNSUPPORTED  # too many boxes without pre_topk
+    d.num_boxes = -1
+    assert L.vkop_cuda_nms_workspace(C.byref(d), C.byref(n)) == capi.INVALID_ARG
+    assert L.vkop_cuda_nms(None, None, None, None, None, None, 0, None) == capi.INVALID_ARG

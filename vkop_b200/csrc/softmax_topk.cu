@@ -48,6 +48,21 @@ struct ChunkParams {
     uint32_t *packets_out;      // non-null: emit one packet per row instead of values/indices
 };
 
+#ifdef VKOP_PHASE_PROF
+// Development aid, compiled only on request: per-CTA timestamps of the kernel's phases.
+__device__ unsigned long long g_phase_prof[16384 * 16];
+__device__ __forceinline__ void prof_mark(int slot) {
+    if (threadIdx.x == 0 && blockIdx.x < 16384) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_phase_prof[blockIdx.x * 16 + slot] = t;
+    }
+}
+#define PROF_MARK(s) prof_mark(s)
+#else
+#define PROF_MARK(s)
+#endif
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -142,6 +157,7 @@ __device__ void select_and_emit(const ChunkParams &p, int64_t row, uint64_t *lis
         work = list;
     }
     // ---- sort groups of 32, then rank every survivor against the other groups ----
+    PROF_MARK(10);
     const int ng = (n2 + 31) / 32;
     for (int g = warp; g < ng; g += NW) {
         const int i = g * 32 + lane;
@@ -150,6 +166,7 @@ __device__ void select_and_emit(const ChunkParams &p, int64_t row, uint64_t *lis
         work[i] = v;
     }
     __syncthreads();
+    PROF_MARK(11);
     for (int g = warp; g < ng; g += NW) {
         const uint64_t me = work[g * 32 + lane];
         int rank = lane;
@@ -305,6 +322,7 @@ __device__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned lo
         }
     }
     __syncthreads();
+    PROF_MARK(8);
     const float M = s_red[0], S = s_red[1];
     const int n = s_int[0];
     // gather: warp per list
@@ -316,6 +334,7 @@ __device__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned lo
             s_buf[off + i] = __ldcg(src + i);
     }
     __syncthreads();
+    PROF_MARK(9);
     const int nsel = n < p.k ? n : p.k;
     if (p.packets_out && tid == 0) {
         uint32_t *pk = p.packets_out + row * packet_words(p.k);
@@ -356,6 +375,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
 
     if (tid == 0)
         s_count = 0;
+    PROF_MARK(0);
 
     // ---- one pass over memory: the chunk lands in registers ----
     uint4 d[VECS];
@@ -403,6 +423,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
             mt = fmaxf(mt, f[e]);
     }
 
+    PROF_MARK(1);
     // ---- threshold: r-th largest thread maximum per full warp, min over warps ----
     const int nfullw = nvc >= THREADS ? NW : nvc / 32;
     const int r = nfullw > 0 ? (p.k + nfullw - 1) / nfullw : 33;
@@ -489,6 +510,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
     __syncthreads();
     const float S = warp_sum(lane < NW ? s_red[lane] : 0.0f);
     int C = s_count;
+    PROF_MARK(2);
 
     // valid elements of this chunk, and how many of them the chunk must deliver
     int64_t e0 = v0 * EPV - head, e1 = v1 * EPV - head;
@@ -532,19 +554,24 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
         mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
         mylist[1] = static_cast<unsigned long long>(C);
     }
+    PROF_MARK(3);
     __threadfence();
     __syncthreads();
+    PROF_MARK(4);
     if (tid == 0) {
         const unsigned int t = atomicAdd(&p.counters[row], 1u);
         s_last = (t == static_cast<unsigned int>(p.splits) - 1u);
     }
     __syncthreads();
+    PROF_MARK(5);
     if (!s_last)
         return;
     __threadfence();
     if (tid == 0)
         p.counters[row] = 0;  // ready for the next launch
     merge_lists<T, THREADS>(p, row, p.lists + row * p.splits * lstride, lstride, p.splits, s_cand, s_red, s_int, s_tmp);
+    __syncthreads();
+    PROF_MARK(6);
 }
 
 // Merge of packets gathered from several GPUs: [shards][rows][packet].
@@ -773,3 +800,9 @@ int launch_merge(const vkop_softmax_topk_desc &d, const void *packets, int shard
 }
 
 }  // namespace vkop_cuda
+
+#ifdef VKOP_PHASE_PROF
+extern "C" int vkop_debug_read_phase_prof(unsigned long long *host, size_t count) {
+    return cudaMemcpyFromSymbol(host, vkop_cuda::g_phase_prof, count * sizeof(unsigned long long)) == cudaSuccess ? 0 : -4;
+}
+#endif
