@@ -1,0 +1,202 @@
+"""CPU tests: the oracle against the golden fixtures and torch-CPU, the reference-emulation variants, and the
+host-side logic that needs no GPU."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import torch
+
+import oracle
+from tests import util
+from vkop_b200 import workloads
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def test_oracle_topk_matches_reference_test_vectors():
+    g = np.load(os.path.join(GOLDEN, "topk_seed56.npz"))
+    for n in range(5):
+        k = int(g[f"case{n}_k"])
+        v, i = oracle.topk(g[f"case{n}_f32_input"], k)
+        assert np.array_equal(i, g[f"case{n}_f32_indices"])
+        assert np.array_equal(v, g[f"case{n}_f32_values"])
+        xh = g[f"case{n}_f16_input"]
+        v, i = oracle.topk(xh, k, dtype=oracle.F16)
+        want = g[f"case{n}_f16_values"].view(np.float16).astype(np.float32)
+        assert np.array_equal(v, want)  # values are tie-order independent
+        st = torch.sort(torch.from_numpy(xh.view(np.float16)).float(), dim=1, stable=True, descending=True)[1][:, :k]
+        assert np.array_equal(i, st.numpy())
+
+
+def test_oracle_softmax_matches_reference_test_vectors():
+    g = np.load(os.path.join(GOLDEN, "softmax_seed42.npz"))
+    for n in range(6):
+        axis = int(g[f"case{n}_axis"])
+        x = g[f"case{n}_f32_input"]
+        y = oracle.softmax(x, axis)
+        want = g[f"case{n}_f32_output"]
+        assert np.all(np.abs(y - want) <= 1e-6 + 1e-5 * np.abs(want))
+        y_seq = oracle.softmax(x, axis, sum_mode=oracle.SUM_F32_SEQUENTIAL)
+        assert np.all(np.abs(y_seq - want) <= 1e-6 + 1e-5 * np.abs(want))
+        xh = g[f"case{n}_f16_input"]
+        yh = oracle.softmax(xh, axis, dtype=oracle.F16)
+        wanth = g[f"case{n}_f16_output"].view(np.float16).astype(np.float32)
+        assert np.all(np.abs(yh - wanth) <= 6e-8 + 2e-3 * np.abs(wanth))
+
+
+def test_oracle_nms_matches_reference_test_expectations():
+    g = np.load(os.path.join(GOLDEN, "nms_cases.npz"))
+    for n in range(3):
+        max_per_class, iou_thr, score_thr = g[f"case{n}_params"]
+        rows, total, per = oracle.nms(g[f"case{n}_boxes"], g[f"case{n}_scores"], iou_threshold=float(iou_thr),
+                                      score_threshold=float(score_thr))
+        want = g[f"case{n}_expected"]
+        assert total == want.shape[0] and np.array_equal(rows, want)
+        if max_per_class > 0:
+            rows2, total2, per2 = oracle.nms(g[f"case{n}_boxes"], g[f"case{n}_scores"], iou_threshold=float(iou_thr),
+                                             score_threshold=float(score_thr),
+                                             max_output_boxes_per_class=int(max_per_class))
+            assert np.all(per2 == np.minimum(per, int(max_per_class)))
+            # per (batch, class) the capped result is a prefix of the uncapped one
+            off = off2 = 0
+            for p_full, p_cap in zip(per, per2):
+                assert np.array_equal(rows[off:off + p_cap], rows2[off2:off2 + p_cap])
+                off += p_full
+                off2 += p_cap
+
+
+def test_oracle_fused_against_torch_on_workloads():
+    for x, k, inv_t in [(workloads.classifier_head(), 5, 1.0), (workloads.batched_classifier(), 5, 1.0),
+                        (workloads.llm_vocab(rows=4), 50, 1.25)]:
+        v, i = oracle.softmax_topk(x.numpy(), k, inv_t)
+        st = torch.sort(x, dim=1, stable=True, descending=True)[1][:, :k]
+        assert np.array_equal(i, st.numpy())
+        p = torch.softmax(x.double() * float(np.float32(inv_t)), -1).gather(1, st).numpy()
+        assert np.all(np.abs(v - p) <= 1e-6 + 1e-5 * np.abs(p))
+        # the reference's own CPU statement (sequential fp32 sum, full sort) agrees on indices and, loosely, on values
+        v2, i2 = oracle.softmax_topk(x.numpy(), k, inv_t, sum_mode=oracle.SUM_F32_SEQUENTIAL, full_sort=True)
+        assert np.array_equal(i2, i)
+        assert np.all(np.abs(v2 - p) <= 1e-6 + 1e-4 * np.abs(p))
+
+
+def test_oracle_ties_zeros_nan_order():
+    x = np.array([[1.0, -0.0, 0.0, 1.0, np.inf, np.nan, -np.inf, 0.0]], np.float32)
+    _, i = oracle.topk(x, 8)
+    assert i[0].tolist() == [5, 4, 0, 3, 1, 2, 7, 6]
+    _, i = oracle.topk(x, 3, largest=False)
+    assert i[0].tolist() == [6, 1, 2]
+    assert oracle.order_key(-0.0) == oracle.order_key(0.0)
+
+
+def test_vocab_sharding_merge_equals_unsharded():
+    x = workloads.sharded_vocab(rows=6, cols=8000)
+    xa = util.to_oracle_array(x)
+    k = 64
+    wv, wi = oracle.softmax_topk(xa, k, dtype=oracle.BF16)
+    from vkop_b200.sharded import split_even
+    for G in (1, 2, 3, 4, 8):
+        packets = []
+        for g in range(G):
+            lo, hi = split_even(x.shape[1], G, g)
+            packets.append(oracle.shard_packet(np.ascontiguousarray(xa[:, lo:hi]), k, lo, dtype=oracle.BF16))
+        v, i = util.merge_packets_reference(packets, k, xa, oracle.BF16)
+        assert np.array_equal(i, wi)
+        assert np.all(np.abs(v - wv) <= 1e-6 + 1e-5 * np.abs(wv))
+
+
+def test_split_even_covers_everything():
+    from vkop_b200.sharded import split_even
+    for n in (0, 1, 7, 64, 256000, 128256):
+        for w in (1, 2, 3, 4, 8):
+            parts = [split_even(n, w, r) for r in range(w)]
+            assert parts[0][0] == 0 and parts[-1][1] == n
+            assert all(parts[r][1] == parts[r + 1][0] for r in range(w - 1))
+            sizes = [b - a for a, b in parts]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_reference_emulation_differences():
+    """Where the reference shaders depart from the canonical contract (kept as documentation of the differences)."""
+    g = torch.Generator().manual_seed(5)
+    # tie-free data: the multi-pass bitonic TopK agrees with the canonical order
+    x = torch.randn(2000, generator=g).numpy()
+    v, i = oracle.ref_topk_bitonic(x, 7)
+    cv, ci = oracle.topk(x[None], 7)
+    assert np.array_equal(i, ci[0]) and np.array_equal(v, cv[0])
+    # tie-heavy data: same values, but equal values come out in network order, not lowest index first
+    differ = 0
+    for t in range(20):
+        xt = (torch.randint(0, 8, (600,), generator=g).float() / 4).numpy()
+        v, i = oracle.ref_topk_bitonic(xt, 7)
+        cv, ci = oracle.topk(xt[None], 7)
+        assert np.array_equal(v, cv[0])
+        differ += int(not np.array_equal(i, ci[0]))
+    assert differ > 0
+    # softmax2.comp's summation tree agrees with the canonical softmax within the contract tolerance
+    row = torch.randn(1000, generator=g).numpy()
+    a, b = oracle.ref_softmax2_row(row), oracle.softmax(row[None])[0]
+    assert np.all(np.abs(a - b) <= 1e-6 + 1e-5 * np.abs(b))
+    # nms.comp on a problem with fewer than 1024 candidates and distinct scores: same kept boxes
+    xy = torch.rand(300, 2, generator=g) * 20
+    boxes = torch.cat([xy, xy + torch.rand(300, 2, generator=g) * 6 + 0.5], -1).numpy()
+    scores = torch.rand(300, generator=g).numpy()
+    kept = oracle.ref_nms_problem(boxes, scores, 0, 0, 0.4, 0.1)
+    rows, _, _ = oracle.nms(boxes[None], scores[None, None], iou_threshold=0.4, score_threshold=0.1)
+    assert np.array_equal(kept, rows[:, 2])
+    # ... and with more than 1024 candidates the shader only considers the first 1024 by index
+    xy = torch.rand(3000, 2, generator=g) * 200
+    boxes = torch.cat([xy, xy + torch.rand(3000, 2, generator=g) * 6 + 0.5], -1).numpy()
+    scores = torch.rand(3000, generator=g).numpy()
+    kept = oracle.ref_nms_problem(boxes, scores, 0, 0, 0.4, 0.1)
+    rows, _, _ = oracle.nms(boxes[None], scores[None, None], iou_threshold=0.4, score_threshold=0.1)
+    assert kept.max() < 1200 and rows[:, 2].max() > 1200
+
+
+def test_c_abi_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "vkop_cuda.h")).read()
+    declared = sorted(set(re.findall(r"\b(vkop_cuda_\w+)\s*\(", header)))
+    assert len(declared) >= 12
+    from vkop_b200 import capi
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert sorted(capi.EXPORTS) == [d for d in declared if d in capi.EXPORTS]
+    missing_binding = [d for d in declared if d not in capi.EXPORTS]
+    assert not missing_binding, missing_binding
+    # calls that need no device
+    assert lib.vkop_cuda_version() == 100
+    lib.vkop_cuda_status_string.restype = ctypes.c_char_p
+    assert lib.vkop_cuda_status_string(-1) == b"VKOP_INVALID_ARG"
+    lib.vkop_cuda_packet_bytes.restype = ctypes.c_size_t
+    assert lib.vkop_cuda_packet_bytes(64) == (4 + 128) * 4
+
+
+def test_workspace_planning_needs_no_device():
+    from vkop_b200 import capi
+    d = capi.SoftmaxTopkDesc(rows=64, cols=128256, row_stride=128256, dtype=capi.F32, k=50, index_dtype=capi.I32,
+                             value_kind=0, inv_temperature=1.25, largest=1, path=0, splits=0, index_offset=0)
+    assert capi.softmax_topk_workspace_bytes(d) > 0
+    d.k = 0
+    n = ctypes.c_size_t()
+    assert capi.lib().vkop_cuda_softmax_topk_workspace(ctypes.byref(d), ctypes.byref(n)) == capi.INVALID_ARG
+    d.k = 1024  # served by the radix path
+    assert capi.softmax_topk_workspace_bytes(d) > 0
+    d.k = 5000
+    assert capi.lib().vkop_cuda_softmax_topk_workspace(ctypes.byref(d), ctypes.byref(n)) == capi.INVALID_ARG
+
+
+def test_product_has_no_cpu_path():
+    from vkop_b200 import capi
+    x = torch.randn(2, 100)
+    try:
+        capi.softmax_topk(x, 5)
+    except RuntimeError as e:
+        assert "CUDA" in str(e)
+    else:
+        raise AssertionError("a CPU tensor must be rejected")
+    src = open(os.path.join(ROOT, "vkop_b200", "capi.py")).read() + open(os.path.join(ROOT, "vkop_b200", "sharded.py")).read()
+    assert "import oracle" not in src and "from oracle" not in src

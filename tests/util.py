@@ -59,3 +59,28 @@ def check_fused(x_cpu: torch.Tensor, k: int, inv_temperature: float = 1.0, what:
     assert_indices_equal(idx, wi, what)
     assert_probs_close(vals, wv, x_cpu.dtype, what)
     return vals, idx
+
+
+def merge_packets_reference(packets, k: int, full_logits: np.ndarray, dtype: int):
+    """Numpy statement of the packet merge (test-side): packets = list of (m, s, keys, idx, count) per shard, as
+    oracle.shard_packet returns them.  Returns (values f32 [rows,k], indices i64 [rows,k])."""
+    rows = packets[0][0].shape[0]
+    vals = np.empty((rows, k), np.float32)
+    idxs = np.empty((rows, k), np.int64)
+    for r in range(rows):
+        M, S = oracle.merge_stats(np.array([p[0][r] for p in packets]), np.array([p[1][r] for p in packets]))
+        cand = []
+        for m, s, keys, idx, cnt in packets:
+            cand += [(-int(keys[r, j]), int(idx[r, j])) for j in range(int(cnt[r]))]
+        cand.sort()
+        best = cand[:k]
+        idxs[r] = [c[1] for c in best]
+        row = full_logits[r:r + 1, idxs[r]]
+        if dtype == oracle.F32:
+            x = row.astype(np.float32)
+        elif dtype == oracle.F16:
+            x = row.view(np.float16).astype(np.float32)
+        else:
+            x = (row.astype(np.uint32) << 16).view(np.float32)
+        vals[r] = (np.exp(x.astype(np.float64)[0] - np.float64(M)) / S).astype(np.float32)
+    return vals, idxs
