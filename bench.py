@@ -192,6 +192,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llm_vocab_f32", choices=sorted(WORKLOADS))
     ap.add_argument("--splits", type=int, default=0, help="chunks per row (0 = automatic)")
+    ap.add_argument("--path", default="auto", choices=["auto", "chunk", "stream", "radix"])
+    ap.add_argument("--serialize", action="store_true",
+                    help="do not declare the resident inputs ready: every launch fully waits for the one before")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
@@ -226,7 +229,10 @@ def main():
     bufs = [h.to(dev) for h in host]
     values = torch.empty((rows, k), dtype=dtype, device=dev)
     indices = torch.empty((rows, k), dtype=torch.int32, device=dev)
-    desc = capi.make_desc(bufs[0], k, inv_t, splits=args.splits)
+    path = {"auto": capi.PATH_AUTO, "chunk": capi.PATH_CHUNK, "stream": capi.PATH_STREAM, "radix": capi.PATH_RADIX}[args.path]
+    # the inputs of every step are resident and complete before the timed region starts
+    flags = 0 if args.serialize else capi.FLAG_INPUT_READY
+    desc = capi.make_desc(bufs[0], k, inv_t, splits=args.splits, path=path, flags=flags)
     ws = capi.Workspace(capi.softmax_topk_workspace_bytes(desc), dev)
 
     import ctypes as C
@@ -296,7 +302,7 @@ def main():
 
         def e2e_step(i):
             stage.copy_(pinned[i % 2], non_blocking=True)
-            capi.softmax_topk(stage, k, inv_t, splits=args.splits, workspace=ws, out=(values, indices))
+            capi.softmax_topk(stage, k, inv_t, splits=args.splits, workspace=ws, out=(values, indices), path=path)
             hv.copy_(values, non_blocking=True)
             hi.copy_(indices, non_blocking=True)
             torch.cuda.current_stream().synchronize()  # the caller reads the result of every step
@@ -347,7 +353,7 @@ def main():
             "config": {"workload": args.workload, "rows_per_gpu": rows, "cols": cols, "k": k, "inv_temperature": inv_t,
                        "sharding": f"rows x{world}" if world > 1 else "none",
                        "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * cols * bufs[0].element_size() >> 20} MiB) > L2",
-                       "splits": int(desc.splits), "launch": "host" if graph is None else f"cuda graph of {NBUF} steps"},
+                       "path": args.path, "input_ready_flag": not args.serialize, "launch": "host" if graph is None else f"cuda graph of {NBUF} steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": abytes, "pct_of_8TBs": achieved / 8000.0 * 100.0},

@@ -46,7 +46,19 @@ typedef enum vkop_status {
 typedef enum vkop_dtype { VKOP_F32 = 0, VKOP_F16 = 1, VKOP_BF16 = 2 } vkop_dtype;
 typedef enum vkop_index_dtype { VKOP_I32 = 0, VKOP_I64 = 1 } vkop_index_dtype;
 typedef enum vkop_value_kind { VKOP_VALUE_PROBABILITY = 0, VKOP_VALUE_RAW = 1 } vkop_value_kind;
-typedef enum vkop_select_path { VKOP_PATH_AUTO = 0, VKOP_PATH_CHUNK = 1, VKOP_PATH_RADIX = 2 } vkop_select_path;
+typedef enum vkop_select_path {
+    VKOP_PATH_AUTO = 0,
+    VKOP_PATH_CHUNK = 1,  /* one CTA per chunk of a row, the chunk held in registers */
+    VKOP_PATH_RADIX = 2,  /* multi-pass radix select (large k, very long rows) */
+    VKOP_PATH_STREAM = 3  /* persistent CTAs streaming tiles with a running threshold */
+} vkop_select_path;
+
+/* The logits are complete and visible before the call is enqueued: no earlier
+ * operation of the same stream still writes them.  The kernel may then start
+ * reading them while the previous kernel of the stream is still draining
+ * (programmatic dependent launch); its own writes still wait for that kernel.
+ * Leave it clear when the logits come from the kernel just before. */
+#define VKOP_FLAG_INPUT_READY 1
 
 /* Library version (VKOP_CUDA_VERSION of the build). */
 int vkop_cuda_version(void);
@@ -85,6 +97,8 @@ typedef struct vkop_softmax_topk_desc {
     int32_t path;          /* vkop_select_path; AUTO picks by k and row length */
     int32_t splits;        /* CTAs per row on the chunk path; 0 = automatic */
     int64_t index_offset;  /* added to every emitted index (offset of a vocabulary shard) */
+    int32_t flags;         /* VKOP_FLAG_* */
+    int32_t reserved;      /* 0 */
 } vkop_softmax_topk_desc;
 
 int vkop_cuda_softmax_topk_workspace(const vkop_softmax_topk_desc *desc, size_t *bytes);

@@ -212,3 +212,97 @@ def test_argument_errors(capi):
     # zero rows is a valid no-op
     z = torch.empty(0, 100).cuda()
     capi.softmax_topk(z, 5)
+
+
+# ---- streaming path (persistent CTAs, running threshold) ----
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_stream_llm_vocab(capi, dtype):
+    x = workloads.llm_vocab(dtype=dtype)
+    util.check_fused(x, workloads.LLM_K, workloads.LLM_INV_TEMPERATURE, what=f"stream C3 {dtype}", path=capi.PATH_STREAM)
+
+
+def test_stream_is_the_automatic_choice_for_large_batches(capi):
+    x = workloads.llm_vocab().cuda()
+    a = capi.softmax_topk(x, 50, 1.25)
+    b = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_STREAM)
+    c = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_CHUNK)
+    torch.cuda.synchronize()
+    assert torch.equal(a[1], b[1]) and torch.equal(a[0], b[0])
+    assert torch.equal(a[1], c[1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stream_odd_shapes(capi, dtype):
+    """CTA ranges that span several rows, unaligned row starts, rows shorter than a tile."""
+    g = torch.Generator().manual_seed(51)
+    for rows, cols, stride, off, k in [(300, 5000, 5000, 0, 9), (37, 20011, 20013, 3, 50), (5, 300007, 300007, 1, 64),
+                                       (1000, 129, 131, 0, 4), (3, 1, 1, 0, 1), (2, 2049, 2049, 0, 128)]:
+        buf = torch.randn(rows * stride + 16, generator=g).to(dtype)
+        x_cpu = buf[off:off + rows * stride].view(rows, stride)[:, :cols]
+        xg = buf.cuda()[off:off + rows * stride].view(rows, stride)[:, :cols]
+        vals, idx = capi.softmax_topk(xg, k, 1.25, path=capi.PATH_STREAM)
+        wv, wi = util.oracle_softmax_topk(x_cpu.contiguous(), k, 1.25)
+        util.assert_indices_equal(idx, wi, f"stream {rows}x{cols} {dtype}")
+        util.assert_probs_close(vals, wv, dtype, f"stream {rows}x{cols} {dtype}")
+
+
+def test_stream_fallback_paths(capi):
+    x = torch.zeros(6, 70000)
+    x[1] = 2.0
+    x[2, 777] = 3.0
+    x[3] = (torch.arange(70000) % 7).float()
+    x[4] = torch.arange(70000).float()           # ascending: the running threshold keeps rising
+    x[5] = -torch.arange(70000).float()
+    util.check_fused(x, 50, what="stream ties", path=capi.PATH_STREAM)
+    y = torch.randn(3, 90000, generator=torch.Generator().manual_seed(52))
+    y[0, 1234] = float("nan")
+    y[0, 80000] = float("nan")
+    y[2, 5] = float("-inf")
+    vals, idx = capi.softmax_topk(y.cuda(), 5, path=capi.PATH_STREAM)
+    wv, wi = util.oracle_softmax_topk(y, 5)
+    util.assert_indices_equal(idx, wi, "stream NaN rows")
+    assert torch.isnan(vals[0]).all() and not torch.isnan(vals[1:]).any()
+
+
+def test_stream_back_to_back_with_input_ready(capi):
+    """Overlapping launches (programmatic dependent launch) on one workspace and one output buffer."""
+    xs = [workloads.llm_vocab(seed=60 + i).cuda() for i in range(3)]
+    d = capi.make_desc(xs[0], 50, 1.25, flags=capi.FLAG_INPUT_READY)
+    ws = capi.Workspace(capi.softmax_topk_workspace_bytes(d))
+    ref = [capi.softmax_topk(x, 50, 1.25, path=capi.PATH_CHUNK) for x in xs]
+    outs = [(torch.empty_like(ref[0][0]), torch.empty_like(ref[0][1])) for _ in xs]
+    torch.cuda.synchronize()
+    for rep in range(20):
+        for x, o in zip(xs, outs):
+            capi.softmax_topk(x, 50, 1.25, workspace=ws, out=o, flags=capi.FLAG_INPUT_READY)
+    torch.cuda.synchronize()
+    for o, r in zip(outs, ref):
+        assert torch.equal(o[1], r[1])
+        assert torch.allclose(o[0], r[0], rtol=1e-5, atol=1e-7)
+    # same buffer for consecutive launches: the last launch wins, nothing is torn
+    o = outs[0]
+    for rep in range(10):
+        for x in xs:
+            capi.softmax_topk(x, 50, 1.25, workspace=ws, out=o, flags=capi.FLAG_INPUT_READY)
+    torch.cuda.synchronize()
+    assert torch.equal(o[1], ref[2][1])
+
+
+def test_stream_raw_smallest_and_packets(capi):
+    g = torch.Generator().manual_seed(53)
+    x = torch.randn(40, 70001, generator=g)
+    xg = x.cuda()
+    v, i = capi.softmax_topk(xg, 11, standalone_topk=True, largest=False, path=capi.PATH_STREAM)
+    wv, wi = oracle.topk(x.numpy(), 11, largest=False)
+    assert np.array_equal(i.cpu().numpy(), wi) and np.array_equal(v.cpu().numpy().view(np.uint32), wv.view(np.uint32))
+    # packets from the streaming path merge like any other
+    xb = workloads.sharded_vocab(rows=24, cols=131072)
+    xbg = xb.cuda()
+    half = xb.shape[1] // 2
+    pk = torch.stack([capi.softmax_topk_partial(xbg[:, :half], 64, 0, path=capi.PATH_STREAM),
+                      capi.softmax_topk_partial(xbg[:, half:], 64, half, path=capi.PATH_STREAM)])
+    vals, idx = capi.softmax_topk_merge(pk, 24, 64, xb.dtype)
+    wv, wi = util.oracle_softmax_topk(xb, 64)
+    util.assert_indices_equal(idx, wi, "stream packets")
+    util.assert_probs_close(vals, wv, xb.dtype, "stream packets")

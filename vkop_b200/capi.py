@@ -17,7 +17,8 @@ LIB_PATH = os.path.join(HERE, "libvkop_cuda.so")
 F32, F16, BF16 = 0, 1, 2
 I32, I64 = 0, 1
 VALUE_PROBABILITY, VALUE_RAW = 0, 1
-PATH_AUTO, PATH_CHUNK, PATH_RADIX = 0, 1, 2
+PATH_AUTO, PATH_CHUNK, PATH_RADIX, PATH_STREAM = 0, 1, 2, 3
+FLAG_INPUT_READY = 1
 OK, INVALID_ARG, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, TIMEOUT = 0, -1, -2, -3, -4, -5
 
 EXPORTS = [
@@ -32,7 +33,7 @@ class SoftmaxTopkDesc(C.Structure):
     _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("row_stride", C.c_int64), ("dtype", C.c_int32),
                 ("k", C.c_int32), ("index_dtype", C.c_int32), ("value_kind", C.c_int32),
                 ("inv_temperature", C.c_float), ("largest", C.c_int32), ("path", C.c_int32), ("splits", C.c_int32),
-                ("index_offset", C.c_int64)]
+                ("index_offset", C.c_int64), ("flags", C.c_int32), ("reserved", C.c_int32)]
 
 
 class SoftmaxDesc(C.Structure):
@@ -123,12 +124,12 @@ class Workspace:
 
 def make_desc(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, index_dtype: int = I32,
               value_kind: int = VALUE_PROBABILITY, largest: bool = True, path: int = PATH_AUTO, splits: int = 0,
-              index_offset: int = 0) -> SoftmaxTopkDesc:
+              index_offset: int = 0, flags: int = 0) -> SoftmaxTopkDesc:
     assert logits.dim() == 2 and logits.stride(1) == 1
     return SoftmaxTopkDesc(rows=logits.shape[0], cols=logits.shape[1], row_stride=logits.stride(0),
                            dtype=dtype_tag(logits), k=k, index_dtype=index_dtype, value_kind=value_kind,
                            inv_temperature=inv_temperature, largest=int(largest), path=path, splits=splits,
-                           index_offset=index_offset)
+                           index_offset=index_offset, flags=flags, reserved=0)
 
 
 def softmax_topk_workspace_bytes(desc: SoftmaxTopkDesc) -> int:
@@ -139,11 +140,12 @@ def softmax_topk_workspace_bytes(desc: SoftmaxTopkDesc) -> int:
 
 def softmax_topk(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, index_dtype: int = I32,
                  value_kind: int = VALUE_PROBABILITY, path: int = PATH_AUTO, splits: int = 0, index_offset: int = 0,
-                 workspace: Workspace | None = None, out=None, standalone_topk: bool = False, largest: bool = True):
+                 workspace: Workspace | None = None, out=None, standalone_topk: bool = False, largest: bool = True,
+                 flags: int = 0):
     """Fused softmax + top-k of a 2-D CUDA tensor.  Returns (values [rows,k] in the logits dtype, indices)."""
     if not logits.is_cuda:
         raise RuntimeError("vkop_b200 runs on CUDA device memory only")
-    desc = make_desc(logits, k, inv_temperature, index_dtype, value_kind, largest, path, splits, index_offset)
+    desc = make_desc(logits, k, inv_temperature, index_dtype, value_kind, largest, path, splits, index_offset, flags)
     need = softmax_topk_workspace_bytes(desc)
     if workspace is None or workspace.nbytes < need:
         workspace = Workspace(need, logits.device)

@@ -26,7 +26,7 @@ static int validate_select(const vkop_softmax_topk_desc *d, bool check_ptrs, con
         return VKOP_INVALID_ARG;
     if (d->row_stride != 0 && d->row_stride < d->cols)
         return VKOP_INVALID_ARG;
-    if (d->path < VKOP_PATH_AUTO || d->path > VKOP_PATH_RADIX || d->splits < 0)
+    if (d->path < VKOP_PATH_AUTO || d->path > VKOP_PATH_STREAM || d->splits < 0)
         return VKOP_INVALID_ARG;
     if (d->index_offset < 0 || d->index_offset + d->cols > 0xFFFFFFFFll)
         return VKOP_INVALID_ARG;
@@ -43,18 +43,38 @@ static int validate_select(const vkop_softmax_topk_desc *d, bool check_ptrs, con
 }
 
 // Chooses the path and sizes the scratch memory.
-static int plan_select(const vkop_softmax_topk_desc &d, SelectPlan *plan) {
-    plan->use_radix = false;
+// `in` is the logits pointer, or null for a size query (then the larger of the aligned / unaligned plans counts).
+static int plan_select(const vkop_softmax_topk_desc &d, const void *in, SelectPlan *plan) {
     int rc = VKOP_UNSUPPORTED;
+    const int64_t row_bytes = d.cols * (d.dtype == VKOP_F32 ? 4 : 2);
+    // rows longer than one CTA's register tile, and enough of them: the streaming kernel
+    const bool prefer_stream = row_bytes > 64 * 1024 && d.rows * row_bytes >= (2ll << 20);
+    if (d.path == VKOP_PATH_STREAM || (d.path == VKOP_PATH_AUTO && prefer_stream && d.splits == 0)) {
+        const bool base_aligned = reinterpret_cast<uintptr_t>(in) % 16 == 0;
+        rc = plan_stream(d, base_aligned, &plan->stream);
+        if (rc == VKOP_OK) {
+            plan->kind = kSelectStream;
+            plan->bytes = plan->stream.counters_bytes + plan->stream.lists_bytes;
+            if (!in) {
+                StreamPlan other;
+                if (plan_stream(d, false, &other) == VKOP_OK && other.counters_bytes + other.lists_bytes > plan->bytes)
+                    plan->bytes = other.counters_bytes + other.lists_bytes;
+            }
+            return VKOP_OK;
+        }
+        if (d.path == VKOP_PATH_STREAM)
+            return rc;
+    }
     if (d.path != VKOP_PATH_RADIX)
         rc = plan_chunk(d, &plan->chunk);
     if (rc == VKOP_OK) {
+        plan->kind = kSelectChunk;
         plan->bytes = plan->chunk.counters_bytes + plan->chunk.packets_bytes;
         return VKOP_OK;
     }
     if (d.path == VKOP_PATH_CHUNK)
         return rc;
-    plan->use_radix = true;
+    plan->kind = kSelectRadix;
     rc = plan_radix(d, &plan->radix);
     if (rc == VKOP_OK)
         plan->bytes = plan->radix.bytes;
@@ -64,7 +84,7 @@ static int plan_select(const vkop_softmax_topk_desc &d, SelectPlan *plan) {
 static int run_select(const vkop_softmax_topk_desc &d, const void *in, void *ov, void *oi, void *packets_out,
                       void *ws, size_t ws_bytes, int need_sum, void *stream) {
     SelectPlan plan;
-    int rc = plan_select(d, &plan);
+    int rc = plan_select(d, in, &plan);
     if (rc != VKOP_OK)
         return rc;
     if (plan.bytes > 0 && (!ws || ws_bytes < plan.bytes))
@@ -72,9 +92,11 @@ static int run_select(const vkop_softmax_topk_desc &d, const void *in, void *ov,
     if (plan.bytes > 0 && reinterpret_cast<uintptr_t>(ws) % 16 != 0)
         return VKOP_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (plan.use_radix)
-        return launch_radix(d, plan.radix, in, ov, oi, packets_out, ws, need_sum, s);
-    return launch_chunk(d, plan.chunk, in, ov, oi, packets_out, ws, need_sum, s);
+    switch (plan.kind) {
+    case kSelectStream: return launch_stream(d, plan.stream, in, ov, oi, packets_out, ws, need_sum, s);
+    case kSelectRadix: return launch_radix(d, plan.radix, in, ov, oi, packets_out, ws, need_sum, s);
+    default: return launch_chunk(d, plan.chunk, in, ov, oi, packets_out, ws, need_sum, s);
+    }
 }
 
 }  // namespace vkop_cuda
@@ -115,7 +137,7 @@ int vkop_cuda_softmax_topk_workspace(const vkop_softmax_topk_desc *desc, size_t 
     if (rc != VKOP_OK)
         return rc;
     SelectPlan plan;
-    rc = plan_select(*desc, &plan);
+    rc = plan_select(*desc, nullptr, &plan);
     if (rc != VKOP_OK)
         return rc;
     *bytes = plan.bytes;

@@ -25,6 +25,18 @@ int launch_chunk(const vkop_softmax_topk_desc &d, const ChunkPlan &plan, const v
 int launch_merge(const vkop_softmax_topk_desc &d, const void *packets, int shards, void *out_values,
                  void *out_indices, cudaStream_t stream);
 
+// ---- streaming path (softmax_topk_stream.cu) ----
+struct StreamPlan {
+    int grid;
+    int64_t per_cta, nvv, vstride;
+    int maxparts, list_cap, parts_per_row, aligned;
+    size_t counters_bytes, lists_bytes, smem_bytes;
+};
+// base_aligned: the logits pointer is a multiple of 16 (rows then are too when the row stride is)
+int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *plan);
+int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const void *logits, void *out_values,
+                  void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream);
+
 // ---- radix path (radix_select.cu) ----
 struct RadixPlan {
     size_t bytes;
@@ -34,9 +46,11 @@ int plan_radix(const vkop_softmax_topk_desc &d, RadixPlan *plan);
 int launch_radix(const vkop_softmax_topk_desc &d, const RadixPlan &plan, const void *logits, void *out_values,
                  void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream);
 
+enum SelectKind { kSelectChunk = 0, kSelectStream = 1, kSelectRadix = 2 };
 struct SelectPlan {
-    bool use_radix;
+    int kind;
     ChunkPlan chunk;
+    StreamPlan stream;
     RadixPlan radix;
     size_t bytes;
 };

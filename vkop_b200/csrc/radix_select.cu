@@ -172,11 +172,10 @@ __global__ void __launch_bounds__(kRadixThreads) radix_hist_kernel(const RadixPa
                 m = vm;
             }
             if (m != -INFINITY) {
-                const float c2 = m * c1;
 #pragma unroll
                 for (int e = 0; e < EPV; e++)
                     if (!ragged || (ibase + e >= 0 && ibase + e < p.cols))
-                        s += ex2f(fmaf(f[e], c1, -c2));
+                        s += ex2f((f[e] - m) * c1);
             }
         }
 #pragma unroll

@@ -1,0 +1,344 @@
+// Device code shared by the fused Softmax + TopK kernels: parameters, the
+// emission of a ranked survivor, the exact selection among candidates held in
+// shared memory, the radix-select fallback over a range of a row, and the
+// per-row merge of published candidate lists.
+#pragma once
+
+#include "common.cuh"
+
+namespace vkop_cuda {
+
+constexpr int kCandCap = 2048;        // candidate slots of the chunk filter
+constexpr int kChunkMaxK = 128;       // largest k served by the chunk path
+constexpr int kMergeMaxSlots = 4096;  // candidates one row may gather for its selection
+constexpr int kListCapMax = 512;      // most candidates one chunk publishes
+
+struct ChunkParams {
+    const void *logits;
+    int64_t rows, cols, row_stride;
+    int k, splits;
+    int vps;        // 16-byte vectors per split
+    int list_cap;   // candidates a chunk may publish (splits > 1)
+    float inv_t;
+    int value_kind, index_dtype, negate, need_sum;
+    int64_t index_offset;
+    void *out_values, *out_indices;
+    unsigned long long *lists;  // [rows][splits][2 + list_cap]: header (m, s, count, -) then candidates
+    unsigned int *counters;     // [rows] arrival counters, zero between launches
+    uint32_t *packets_out;      // non-null: emit one packet per row instead of values/indices
+    // streaming kernel only
+    int64_t nvv;       // vector slots per row (the same for every row; slots past a row's end are empty)
+    int64_t per_cta;   // nominal vector slots per CTA
+    int64_t vstride;   // vectors between the starts of consecutive rows (rows 16-byte aligned only)
+    int parts_per_row; // > 0: every row is cut into this many CTAs and no CTA crosses a row
+    int input_ready;   // the logits were complete before this launch was enqueued
+};
+
+#ifdef VKOP_PHASE_PROF
+// Development aid, compiled only on request: per-CTA timestamps of the kernel's phases.
+static __device__ unsigned long long g_phase_prof[16384 * 16];
+__device__ __forceinline__ void prof_mark(int slot) {
+    if (threadIdx.x == 0 && blockIdx.x < 16384) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_phase_prof[blockIdx.x * 16 + slot] = t;
+    }
+}
+#define PROF_MARK(s) prof_mark(s)
+#else
+#define PROF_MARK(s)
+#endif
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Where a ranked survivor goes: the final outputs, a packet, or a candidate list.
+template <typename T>
+__device__ __forceinline__ void emit(const ChunkParams &p, int64_t row, int rank, uint64_t comp, float m, float s,
+                                     unsigned long long *list_out) {
+    if (list_out) {
+        list_out[rank] = comp;
+        return;
+    }
+    const uint32_t idx = cand_idx(comp);
+    if (p.packets_out) {
+        uint32_t *pk = p.packets_out + row * packet_words(p.k);
+        pk[4 + rank] = cand_key(comp);
+        pk[4 + p.k + rank] = idx + static_cast<uint32_t>(p.index_offset);
+        return;
+    }
+    const int64_t o = row * p.k + rank;
+    if (p.value_kind == VKOP_VALUE_RAW) {
+        reinterpret_cast<T *>(p.out_values)[o] = reinterpret_cast<const T *>(p.logits)[row * p.row_stride + idx];
+    } else {
+        store_value<T>(p.out_values, o, softmax_prob(key_to_float(cand_key(comp)), p.inv_t, m, s));
+    }
+    store_index(p.out_indices, p.index_dtype, o, static_cast<int64_t>(idx) + p.index_offset);
+}
+
+// Warp bitonic sort of one 64-bit value per lane, descending by lane.
+__device__ __forceinline__ uint64_t warp_sort_desc(uint64_t v, int lane) {
+#pragma unroll
+    for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const uint64_t other = __shfl_xor_sync(kFullMask, v, stride);
+            const bool desc_block = (lane & size) == 0;
+            const bool low_lane = (lane & stride) == 0;
+            const uint64_t hi = v > other ? v : other, lo = v > other ? other : v;
+            v = (desc_block == low_lane) ? hi : lo;
+        }
+    }
+    return v;
+}
+
+// Exact selection of the best min(k, n) of n distinct candidates held in shared
+// memory (list[0..n)); `work` is a second region of at least n slots.  The
+// survivors are emitted at their rank.  Executed by the whole CTA; list and
+// work are clobbered.
+template <typename T, int THREADS>
+__device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, uint64_t *list, int n, uint64_t *work, float M,
+                                float S, unsigned long long *list_out, int *s_tmp) {
+    constexpr int NW = THREADS / 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k = p.k;
+    // ---- narrow: r-th largest key of every full group of 32, minimised over the groups; the survivors
+    // are regrouped and narrowed again while that still removes a good share of them ----
+    uint64_t *src = list;
+    int n2 = n;
+    for (int round = 0; round < 4; round++) {
+        const int nfull = n2 / 32;
+        const int r = nfull > 0 ? (k + nfull - 1) / nfull : 99;
+        if (!(n2 > 2 * k + 32 && r <= 8))
+            break;
+        if (tid == 0) {
+            s_tmp[0] = 0x7FFFFFFF;  // threshold key >> 1 (kept positive for atomicMin on int)
+            s_tmp[1] = 0;
+        }
+        __syncthreads();
+        for (int g = warp; g < nfull; g += NW) {
+            uint32_t cur = cand_key(src[g * 32 + lane]);
+            uint32_t rth = 0;
+            for (int i = 0; i < r; i++) {
+                rth = __reduce_max_sync(kFullMask, cur);
+                const unsigned b = __ballot_sync(kFullMask, cur == rth);
+                if (lane == __ffs(b) - 1)
+                    cur = 0;
+            }
+            if (lane == 0)
+                atomicMin(&s_tmp[0], static_cast<int>(rth >> 1));
+        }
+        __syncthreads();
+        const uint32_t tkey = static_cast<uint32_t>(s_tmp[0]) << 1;  // rounded down: keeps the bound valid
+        for (int i = tid; i < n2; i += THREADS) {
+            const uint64_t c = src[i];
+            if (cand_key(c) >= tkey) {
+                const int pos = atomicAdd(&s_tmp[1], 1);
+                work[pos] = c;
+            }
+        }
+        __syncthreads();
+        const int n3 = s_tmp[1];
+        uint64_t *t = src;
+        src = work;
+        work = t;
+        const bool progress = n3 * 4 <= n2 * 3;
+        n2 = n3;
+        __syncthreads();  // s_tmp is reused by the next round
+        if (!progress)
+            break;
+    }
+    // ---- sort groups of 32, then rank every survivor against the other groups ----
+    PROF_MARK(10);
+    const int ng = (n2 + 31) / 32;
+    for (int g = warp; g < ng; g += NW) {
+        const int i = g * 32 + lane;
+        uint64_t v = i < n2 ? src[i] : 0ull;
+        v = warp_sort_desc(v, lane);
+        work[i] = v;
+    }
+    __syncthreads();
+    PROF_MARK(11);
+    for (int g = warp; g < ng; g += NW) {
+        const uint64_t me = work[g * 32 + lane];
+        int rank = lane;
+        if (me != 0ull) {
+            for (int o = 0; o < ng && rank < k; o++) {
+                if (o == g)
+                    continue;
+                const uint64_t *a = work + o * 32;
+                int lo = 0, hi = 32;
+#pragma unroll
+                for (int step = 0; step < 6; step++) {
+                    if (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (a[mid] > me)
+                            lo = mid + 1;
+                        else
+                            hi = mid;
+                    }
+                }
+                rank += lo;
+            }
+            if (rank < k)
+                emit<T>(p, row, rank, me, M, S, list_out);
+        }
+    }
+}
+
+// Exact selection of the kk best (key, ~index) values of a chunk by an 8-bit
+// most-significant-digit radix select over the 64-bit candidate value.  The
+// chunk is re-read from memory.  Leaves exactly kk candidates in s_cand.
+template <typename T, int THREADS>
+__device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int64_t v1, int head, int64_t cols,
+                                             int negate, int kk, uint64_t *s_cand, int *s_count, int *s_hist,
+                                             int *s_pick) {
+    constexpr int EPV = Elem<T>::kPerVec;
+    const int tid = threadIdx.x;
+    uint64_t prefix = 0, mask = 0;
+    int need = kk;
+    for (int pass = 7; pass >= 0; --pass) {
+        const int shift = pass * 8;
+        for (int i = tid; i < 256; i += THREADS)
+            s_hist[i] = 0;
+        __syncthreads();
+        for (int64_t v = v0 + tid; v < v1; v += THREADS) {
+            uint4 d = vbase[v];
+            if (negate) {
+                const uint32_t x = sizeof(T) == 4 ? 0x80000000u : 0x80008000u;
+                d.x ^= x; d.y ^= x; d.z ^= x; d.w ^= x;
+            }
+            float f[EPV];
+            Elem<T>::unpack(d, f);
+#pragma unroll
+            for (int e = 0; e < EPV; e++) {
+                int64_t i = v * EPV + e - head;
+                if (i >= 0 && i < cols) {
+                    uint64_t c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                    if ((c & mask) == prefix)
+                        atomicAdd(&s_hist[static_cast<int>(c >> shift) & 255], 1);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int cum = 0, d = 255;
+            for (; d > 0; --d) {
+                int c = s_hist[d];
+                if (cum + c >= need)
+                    break;
+                cum += c;
+            }
+            s_pick[0] = d;
+            s_pick[1] = need - cum;
+            s_pick[2] = s_hist[d];
+        }
+        __syncthreads();
+        prefix |= static_cast<uint64_t>(s_pick[0]) << shift;
+        mask |= 0xFFull << shift;
+        need = s_pick[1];
+        if (s_pick[2] == need)
+            break;  // the whole bin is taken: threshold = prefix
+    }
+    if (tid == 0)
+        *s_count = 0;
+    __syncthreads();
+    for (int64_t v = v0 + tid; v < v1; v += THREADS) {
+        uint4 d = vbase[v];
+        if (negate) {
+            const uint32_t x = sizeof(T) == 4 ? 0x80000000u : 0x80008000u;
+            d.x ^= x; d.y ^= x; d.z ^= x; d.w ^= x;
+        }
+        float f[EPV];
+        Elem<T>::unpack(d, f);
+#pragma unroll
+        for (int e = 0; e < EPV; e++) {
+            int64_t i = v * EPV + e - head;
+            if (i >= 0 && i < cols) {
+                uint64_t c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                if (c >= prefix) {
+                    int pos = atomicAdd(s_count, 1);
+                    if (pos < kCandCap)
+                        s_cand[pos] = c;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// Gathers the candidate lists of the G parts of one row into shared memory,
+// merges their statistics and selects.  Executed by one whole CTA.
+// lists: G blocks of `stride` 64-bit words: header word 0 = (m, s) as float
+// bits, header word 1 = count; then the candidates.
+template <typename T, int THREADS>
+__device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned long long *lists, int64_t stride, int G,
+                            uint64_t *s_buf, float *s_red, int *s_int, int *s_tmp) {
+    constexpr int NW = THREADS / 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // statistics and list offsets (one warp walks the headers)
+    if (warp == 0) {
+        float m = -INFINITY;
+        for (int g = lane; g < G; g += 32)
+            m = fmaxf(m, __uint_as_float(static_cast<uint32_t>(__ldcg(lists + g * stride))));
+        m = warp_max(m);
+        float s = 0.0f;
+        int base = 0;
+        for (int g0 = 0; g0 < G; g0 += 32) {
+            const int g = g0 + lane;
+            int cnt = 0;
+            if (g < G) {
+                const unsigned long long h = __ldcg(lists + g * stride);
+                const float mg = __uint_as_float(static_cast<uint32_t>(h));
+                const float sg = __uint_as_float(static_cast<uint32_t>(h >> 32));
+                if (sg != 0.0f)  // an all -inf part has sum 0 and no defined maximum
+                    s += sg * expf(mg - m);
+                cnt = static_cast<int>(__ldcg(lists + g * stride + 1));
+            }
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(kFullMask, incl, o);
+                if (lane >= o)
+                    incl += v;
+            }
+            if (g < G)
+                s_int[8 + g] = base + incl - cnt;  // offset of list g
+            base += __shfl_sync(kFullMask, incl, 31);
+        }
+        s = warp_sum(s);
+        if (lane == 0) {
+            s_red[0] = m;
+            s_red[1] = s;
+            s_int[0] = base;
+        }
+    }
+    __syncthreads();
+    PROF_MARK(8);
+    const float M = s_red[0], S = s_red[1];
+    const int n = s_int[0];
+    // gather: warp per list
+    for (int g = warp; g < G; g += NW) {
+        const int off = s_int[8 + g];
+        const int end = (g + 1 < G) ? s_int[8 + g + 1] : n;
+        const unsigned long long *src = lists + g * stride + 2;
+        for (int i = lane; i < end - off; i += 32)
+            s_buf[off + i] = __ldcg(src + i);
+    }
+    __syncthreads();
+    PROF_MARK(9);
+    const int nsel = n < p.k ? n : p.k;
+    if (p.packets_out && tid == 0) {
+        uint32_t *pk = p.packets_out + row * packet_words(p.k);
+        pk[0] = __float_as_uint(M);
+        pk[1] = __float_as_uint(S);
+        pk[2] = static_cast<uint32_t>(nsel);
+        pk[3] = 0;
+    }
+    select_and_emit<T, THREADS>(p, row, s_buf, n, s_buf + ((n + 31) & ~31), M, S, nullptr, s_tmp);
+}
+
+}  // namespace vkop_cuda
