@@ -35,13 +35,15 @@ struct ChunkParams {
 };
 
 #ifdef VKOP_PHASE_PROF
-// Development aid, compiled only on request: per-CTA timestamps of the kernel's phases.
-static __device__ unsigned long long g_phase_prof[16384 * 16];
+// Development aid, compiled only on request: per-CTA timestamps of the kernels' phases, for the last
+// eight launches (slot = launch sequence number modulo 8).
+static __device__ unsigned long long g_phase_prof[8 * 1024 * 16];
+static __device__ int g_phase_seq;
 __device__ __forceinline__ void prof_mark(int slot) {
-    if (threadIdx.x == 0 && blockIdx.x < 16384) {
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_phase_prof[blockIdx.x * 16 + slot] = t;
+        g_phase_prof[((g_phase_seq & 7) * 1024 + blockIdx.x) * 16 + slot] = t;
     }
 }
 #define PROF_MARK(s) prof_mark(s)
@@ -279,57 +281,112 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
                             uint64_t *s_buf, float *s_red, int *s_int, int *s_tmp) {
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // statistics and list offsets (one warp walks the headers)
-    if (warp == 0) {
-        float m = -INFINITY;
-        for (int g = lane; g < G; g += 32)
-            m = fmaxf(m, __uint_as_float(static_cast<uint32_t>(__ldcg(lists + g * stride))));
-        m = warp_max(m);
-        float s = 0.0f;
-        int base = 0;
-        for (int g0 = 0; g0 < G; g0 += 32) {
-            const int g = g0 + lane;
-            int cnt = 0;
-            if (g < G) {
-                const unsigned long long h = __ldcg(lists + g * stride);
-                const float mg = __uint_as_float(static_cast<uint32_t>(h));
-                const float sg = __uint_as_float(static_cast<uint32_t>(h >> 32));
-                if (sg != 0.0f)  // an all -inf part has sum 0 and no defined maximum
-                    s += sg * expf(mg - m);
-                cnt = static_cast<int>(__ldcg(lists + g * stride + 1));
-            }
-            int incl = cnt;
+    float M, S;
+    int n;
+    if (G <= NW && p.list_cap <= 512) {
+        // Few, short lists: warp g takes list g and fetches its header and its whole capacity in one
+        // round trip (entries past the count are ignored); one barrier later every warp knows all counts
+        // and drops its entries at the right offset.
+        const int g = warp;
+        unsigned long long regs[16];
+        int cnt = 0;
+        if (g < G) {
+            const unsigned long long *L = lists + g * stride;
+            const unsigned long long h0 = __ldcg(L), h1 = __ldcg(L + 1);
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(kFullMask, incl, o);
-                if (lane >= o)
-                    incl += v;
+            for (int j = 0; j < 16; j++) {
+                const int i = lane + 32 * j;
+                regs[j] = i < p.list_cap ? __ldcg(L + 2 + i) : 0ull;
             }
-            if (g < G)
-                s_int[8 + g] = base + incl - cnt;  // offset of list g
-            base += __shfl_sync(kFullMask, incl, 31);
+            cnt = static_cast<int>(h1);
+            if (lane == 0) {
+                s_int[8 + g] = cnt;
+                s_int[8 + NW + g] = static_cast<int>(static_cast<uint32_t>(h0));         // max z bits
+                s_int[8 + 2 * NW + g] = static_cast<int>(static_cast<uint32_t>(h0 >> 32));  // sum bits
+            }
         }
-        s = warp_sum(s);
-        if (lane == 0) {
-            s_red[0] = m;
-            s_red[1] = s;
-            s_int[0] = base;
+        __syncthreads();
+        PROF_MARK(8);
+        int off = 0;
+        n = 0;
+        M = -INFINITY;
+        for (int q = 0; q < G; q++) {
+            const int c = s_int[8 + q];
+            if (q < g)
+                off += c;
+            n += c;
+            M = fmaxf(M, __int_as_float(s_int[8 + NW + q]));
         }
+        S = 0.0f;
+        for (int q = 0; q < G; q++) {
+            const float sg = __int_as_float(s_int[8 + 2 * NW + q]);
+            if (sg != 0.0f)  // an all -inf part has sum 0 and no defined maximum
+                S += sg * expf(__int_as_float(s_int[8 + NW + q]) - M);
+        }
+        if (g < G) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int i = lane + 32 * j;
+                if (i < cnt)
+                    s_buf[off + i] = regs[j];
+            }
+        }
+        __syncthreads();
+        PROF_MARK(9);
+    } else {
+        // statistics and list offsets (one warp walks the headers)
+        if (warp == 0) {
+            float m = -INFINITY;
+            for (int g = lane; g < G; g += 32)
+                m = fmaxf(m, __uint_as_float(static_cast<uint32_t>(__ldcg(lists + g * stride))));
+            m = warp_max(m);
+            float s = 0.0f;
+            int base = 0;
+            for (int g0 = 0; g0 < G; g0 += 32) {
+                const int g = g0 + lane;
+                int cnt = 0;
+                if (g < G) {
+                    const unsigned long long h = __ldcg(lists + g * stride);
+                    const float mg = __uint_as_float(static_cast<uint32_t>(h));
+                    const float sg = __uint_as_float(static_cast<uint32_t>(h >> 32));
+                    if (sg != 0.0f)  // an all -inf part has sum 0 and no defined maximum
+                        s += sg * expf(mg - m);
+                    cnt = static_cast<int>(__ldcg(lists + g * stride + 1));
+                }
+                int incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(kFullMask, incl, o);
+                    if (lane >= o)
+                        incl += v;
+                }
+                if (g < G)
+                    s_int[8 + g] = base + incl - cnt;  // offset of list g
+                base += __shfl_sync(kFullMask, incl, 31);
+            }
+            s = warp_sum(s);
+            if (lane == 0) {
+                s_red[0] = m;
+                s_red[1] = s;
+                s_int[0] = base;
+            }
+        }
+        __syncthreads();
+        PROF_MARK(8);
+        M = s_red[0];
+        S = s_red[1];
+        n = s_int[0];
+        // gather: warp per list
+        for (int g = warp; g < G; g += NW) {
+            const int off = s_int[8 + g];
+            const int end = (g + 1 < G) ? s_int[8 + g + 1] : n;
+            const unsigned long long *src = lists + g * stride + 2;
+            for (int i = lane; i < end - off; i += 32)
+                s_buf[off + i] = __ldcg(src + i);
+        }
+        __syncthreads();
+        PROF_MARK(9);
     }
-    __syncthreads();
-    PROF_MARK(8);
-    const float M = s_red[0], S = s_red[1];
-    const int n = s_int[0];
-    // gather: warp per list
-    for (int g = warp; g < G; g += NW) {
-        const int off = s_int[8 + g];
-        const int end = (g + 1 < G) ? s_int[8 + g + 1] : n;
-        const unsigned long long *src = lists + g * stride + 2;
-        for (int i = lane; i < end - off; i += 32)
-            s_buf[off + i] = __ldcg(src + i);
-    }
-    __syncthreads();
-    PROF_MARK(9);
     const int nsel = n < p.k ? n : p.k;
     if (p.packets_out && tid == 0) {
         uint32_t *pk = p.packets_out + row * packet_words(p.k);

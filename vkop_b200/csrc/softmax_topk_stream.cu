@@ -1,14 +1,15 @@
-// Fused Softmax + TopK, streaming path: the kernel for large batches.
+// Fused Softmax + TopK, streaming path: the kernels for large batches.
 //
-// A fixed grid of CTAs (all resident at once, two per SM) splits the whole
-// [rows, cols] tensor by bytes.  Every CTA owns one contiguous range of
-// 16-byte vector slots; range boundaries are snapped to multiples of 256
-// vectors inside a row, so that a CTA never holds a sliver of a row, and with
-// few rows every row is cut into the same number of CTAs and no CTA crosses a
-// row.  A CTA walks its range in tiles; the loads of the next tile are issued
-// before the current tile is processed, so the memory system always has a
-// tile per thread in flight while the arithmetic runs (software pipelining in
-// registers; no spin-wait anywhere).
+// Kernel 1 (stream).  A fixed grid of CTAs, all resident at once (two per SM),
+// splits the whole [rows, cols] tensor by bytes.  Every CTA owns one contiguous
+// range of 16-byte vector slots; range boundaries are snapped to multiples of
+// 256 vectors inside a row, so that a CTA never holds a sliver of a row, and
+// with few rows every row is cut into the same number of CTAs and no CTA
+// crosses a row.  A CTA walks its range in tiles that are staged through
+// shared memory with cp.async, two stages deep: the copy of the next tile is
+// in flight while the current one is processed, every thread copies into and
+// reads back its own slots only, and the only wait is the hardware wait on the
+// thread's own copy groups (no spin-wait anywhere).
 //
 // Per tile and thread: the maximum of its elements updates a running maximum
 // m_t and rescales a running exp-sum s_t (online softmax); the r-th largest
@@ -17,19 +18,22 @@
 // stays in one row; elements >= T are appended to a candidate list in shared
 // memory.  Early tiles pass a hundred candidates, later ones a handful.
 //
-// When a CTA leaves a row (or its range ends) it publishes that row part:
-// statistics and candidates go to global scratch, then one thread adds the
-// part's length to the row's progress counter while the CTA already streams on;
-// the part that completes a row gathers all parts of the row and selects the k
-// best (select.cuh) at the next tile boundary.
+// When a CTA leaves a row (or its range ends) it finishes that row part: the
+// statistics are reduced over the CTA, candidates below the final threshold
+// are dropped, and the part is published to global scratch with plain stores.
+// The CTA then streams on or retires; it never waits for another CTA.
 //
-// The kernel is launched with programmatic stream serialization: it lets the
-// next kernel of the stream start while it drains (griddepcontrol.launch_dependents
-// on entry) and itself waits for the previous kernel (griddepcontrol.wait)
-// before it reads the logits -- or, when the caller states that the logits
-// were complete before the launch, only before its first write to scratch
-// memory or outputs, so that back-to-back calls overlap launch latency and the
-// selection tail with streaming.
+// Kernel 2 (select), one light CTA per row, gathers the parts of its row,
+// merges their statistics and selects the k best (select.cuh).
+//
+// Both kernels are launched with programmatic stream serialization.  Each lets
+// its successor start early (griddepcontrol.launch_dependents on entry) and
+// waits for its predecessor (griddepcontrol.wait) before it touches memory the
+// predecessor may still use: the select kernel at once, the stream kernel
+// before it reads the logits -- or, when the caller states that the logits were
+// complete before the call, only before its first write to scratch memory.
+// Back-to-back calls then overlap: while the select kernel of one call works,
+// the stream kernel of the next call already pulls its logits from HBM.
 #include "common.cuh"
 #include "launchers.h"
 #include "select.cuh"
@@ -40,7 +44,10 @@ constexpr int kStreamThreads = 512;
 constexpr int kStreamVecs = 4;
 constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
-constexpr int kUnit = 256;  // range boundaries inside a row are multiples of this many vectors
+constexpr int kUnit = 256;            // range boundaries inside a row are multiples of this many vectors
+constexpr int kStreamCandCap = 2048;  // candidate slots of one row part
+constexpr int kStreamListCap = 512;   // most candidates one row part publishes
+constexpr int kSelectThreads = 256;
 
 // Snaps a slot offset inside a row to the nearest allowed boundary.
 __host__ __device__ inline uint32_t snap_in_row(uint32_t v, uint32_t nvv) {
@@ -90,18 +97,17 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     constexpr int EPV = Elem<T>::kPerVec;
     constexpr int NW = THREADS / 32;
     constexpr int TV = THREADS * VECS;  // vectors per tile
+    constexpr int CAP = kStreamCandCap;
     extern __shared__ __align__(16) uint64_t s_dyn[];
-    uint64_t *s_cand = s_dyn;                   // candidates of the current row part: kCandCap slots
-    uint64_t *s_work = s_dyn + kCandCap;        // second region for the in-CTA selection: kCandCap slots
-    uint64_t *s_merge = s_dyn + 2 * kCandCap;   // gather buffer of a row selection
+    uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);  // two tile stages of TV vectors
+    uint64_t *s_cand = s_dyn + 2 * TV * 2;              // candidates of the current row part: CAP slots
+    uint64_t *s_work = s_cand + CAP;                    // second region: filtered list / in-CTA selection
     __shared__ uint32_t s_wr[2][NW], s_wm[2][NW];
     __shared__ float s_red[NW];
-    __shared__ int s_int[8 + 1024];
     __shared__ int s_hist[256];
     __shared__ int s_pick[4];
     __shared__ int s_tmp[2];
     __shared__ int s_count;
-    __shared__ int s_merge_row;  // row this CTA has to select for, or -1
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     asm volatile("griddepcontrol.launch_dependents;");
@@ -148,19 +154,49 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         nvt = remaining;
     bool part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
 
+    auto issue_tile = [&](int stage, int r, int tv0, int tn) {
+        int head, nvr;
+        const uint4 *vbase;
+        row_geom(r, head, nvr, vbase);
+        const int lim = tn < nvr - tv0 ? tn : nvr - tv0;
+        const uint4 *src = vbase + tv0;
+        uint4 *dst = s_tile + stage * TV;
+#pragma unroll
+        for (int j = 0; j < VECS; j++) {
+            const int lv = j * THREADS + tid;
+            if (lv < lim) {
+                const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(dst + lv));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + lv) : "memory");
+            } else {
+                dst[lv] = make_uint4(filler, filler, filler, filler);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int stage = 0;
+    issue_tile(0, row, v0, nvt);
     PROF_MARK(0);
 
     // ---- state of the current row part ----
+    // Threshold groups: gs lanes form a group; the minimum over all groups (of full warps) of the group
+    // maximum of the running thread maxima has at least one element per group at or above it, so gs is
+    // the largest power of two that still gives k groups (0: the part is too small for a threshold).
+    auto group_lanes = [&](int full_warps) {
+        int g = 32;
+        while (g >= 1 && full_warps * (32 / g) < p.k)
+            g >>= 1;
+        return g;
+    };
     float m_t = -INFINITY, s_t = 0.0f;
-    uint32_t tkey = 0;       // running threshold key (0 = none yet)
+    uint32_t tkey = 0;       // running threshold key (0 = none yet: every valid element is a candidate)
+    float T_thr = key_to_float(0u);
     int part_v0 = v0;        // first slot of the part
+    int part_tile = 0;       // tiles of the part processed so far
     int nfullw = (nvt < THREADS ? nvt : THREADS) / 32;  // warps whose threads all own data in this part
-    int r_sel = nfullw > 0 ? (p.k + nfullw - 1) / nfullw : 33;
+    int gs = group_lanes(nfullw);
     int parity = 0;
-    if (tid == 0) {
+    if (tid == 0)
         s_count = 0;
-        s_merge_row = -1;
-    }
     __syncthreads();
 
     for (;;) {
@@ -170,22 +206,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         int head, nvr;
         const uint4 *vbase;
         row_geom(c_row, head, nvr, vbase);
-        // The tile: VECS independent 16-byte loads per thread.  With 32 resident warps per SM the loads of
-        // the other warps and of the other CTA cover the latency; no register double buffering is needed.
-        uint4 d[VECS];
-        {
-            const int lim = c_nvt < nvr - c_v0 ? c_nvt : nvr - c_v0;
-            const uint4 *src = vbase + c_v0;
-#pragma unroll
-            for (int j = 0; j < VECS; j++) {
-                const int lv = j * THREADS + tid;
-                if (lv < lim)
-                    d[j] = load_stream(src + lv);
-                else
-                    d[j] = make_uint4(filler, filler, filler, filler);
-            }
-        }
-        // advance the iterator
+        // advance the iterator and start the copy of the next tile into the other stage
         remaining -= nvt;
         const bool has_next = remaining > 0;
         if (has_next) {
@@ -198,7 +219,20 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             if (nvt > remaining)
                 nvt = remaining;
             part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
+            issue_tile(stage ^ 1, row, v0, nvt);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the copy just started
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
+        // the current tile: this thread's own slots of the stage
+        uint4 d[VECS];
+        {
+            const uint4 *src = s_tile + stage * TV;
+#pragma unroll
+            for (int j = 0; j < VECS; j++)
+                d[j] = src[j * THREADS + tid];
+        }
+        stage ^= 1;
 
         if (p.negate) {
             const uint32_t x = sizeof(T) == 4 ? 0x80000000u : 0x80008000u;
@@ -223,15 +257,19 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             }
         }
 
-        // ---- tile maximum of this thread; online softmax statistics ----
+        // ---- maxima per vector and of the tile; online softmax statistics ----
+        float vmax[VECS];
         float vm = -INFINITY;
 #pragma unroll
         for (int j = 0; j < VECS; j++) {
             float f[EPV];
             Elem<T>::unpack(d[j], f);
+            float a = f[0];
 #pragma unroll
-            for (int e = 0; e < EPV; e++)
-                vm = fmaxf(vm, f[e]);
+            for (int e = 1; e < EPV; e++)
+                a = fmaxf(a, f[e]);
+            vmax[j] = a;
+            vm = fmaxf(vm, a);
         }
         if (vm > m_t) {
             s_t *= ex2_approx((m_t - vm) * c1);
@@ -249,60 +287,50 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             }
         }
 
-        // ---- threshold refresh from the running thread maxima (and the part maximum) ----
-        {
-            uint32_t cur = order_key(m_t);
-            const uint32_t wmax = __reduce_max_sync(kFullMask, cur);
-            uint32_t rth = 0;
-            if (r_sel <= 32) {
-                if (warp < nfullw) {
-                    for (int i = 0; i < r_sel; i++) {
-                        rth = __reduce_max_sync(kFullMask, cur);
-                        const unsigned b = __ballot_sync(kFullMask, cur == rth);
-                        if (lane == __ffs(b) - 1)
-                            cur = 0;
-                    }
-                } else {
-                    rth = 0xFFFFFFFFu;
+        // ---- threshold refresh from the running thread maxima: on tiles 0, 1, 3, 7, ... of the part and
+        // on its last tile (the threshold settles quickly); the other tiles need no barrier at all ----
+        if ((part_tile & (part_tile + 1)) == 0 || c_last) {
+            uint32_t key = order_key(m_t);
+            if (gs > 0 && warp < nfullw) {
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t other = __shfl_xor_sync(kFullMask, key, o);
+                    key = o < gs ? max(key, other) : min(key, other);  // maximum inside a group, minimum over groups
                 }
+            } else {
+                key = gs > 0 ? 0xFFFFFFFFu : 0u;  // a partly filled warp does not constrain the threshold
             }
-            if (lane == 0) {
-                s_wr[parity][warp] = rth;
-                s_wm[parity][warp] = wmax;
-            }
-        }
-        __syncthreads();
-        const uint32_t t_new = __reduce_min_sync(kFullMask, lane < NW ? s_wr[parity][lane] : 0xFFFFFFFFu);
-        tkey = t_new > tkey ? t_new : tkey;
-        const float T_thr = key_to_float(tkey);
-        const bool allpass = tkey == 0u || T_thr == -INFINITY;
-
-        // a row selection handed to this CTA by an earlier part's completion (published before the barrier above)
-        if (s_merge_row >= 0) {
-            const int mrow = s_merge_row;
-            const uint32_t cf = stream_owner(static_cast<uint32_t>(mrow) * nvv, grid, per, nvv, total, parts);
-            const uint32_t cl = stream_owner(static_cast<uint32_t>(mrow + 1) * nvv - 1, grid, per, nvv, total, parts);
-            merge_lists<T, THREADS>(p, mrow, p.lists + static_cast<int64_t>(mrow) * p.splits * lstride, lstride,
-                                    static_cast<int>(cl - cf + 1), s_merge, s_red, s_int, s_tmp);
+            if (lane == 0)
+                s_wr[parity][warp] = key;
             __syncthreads();
-            if (tid == 0)
-                s_merge_row = -1;
+            uint32_t t_new = lane < NW ? s_wr[parity][lane] : 0xFFFFFFFFu;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1)
+                t_new = min(t_new, __shfl_xor_sync(kFullMask, t_new, o));
+            tkey = t_new > tkey ? t_new : tkey;
+            T_thr = key_to_float(tkey);
+            parity ^= 1;
         }
+        part_tile++;
+        const bool allpass = tkey == 0u || T_thr == -INFINITY;
 
         // ---- candidates of this tile ----
         if (!allpass) {
+            // padding is -inf and T is above -inf: whatever passes is a valid element
             if (!(vm < T_thr)) {
 #pragma unroll
                 for (int j = 0; j < VECS; j++) {
-                    float f[EPV];
-                    Elem<T>::unpack(d[j], f);
+                    if (!(vmax[j] < T_thr)) {
+                        float f[EPV];
+                        Elem<T>::unpack(d[j], f);
 #pragma unroll
-                    for (int e = 0; e < EPV; e++) {
-                        if (!(f[e] < T_thr)) {
-                            const int pos = atomicAdd(&s_count, 1);
-                            if (pos < kCandCap)
-                                s_cand[pos] = make_cand(order_key(f[e]),
-                                                        static_cast<uint32_t>((c_v0 + j * THREADS + tid) * EPV + e - head));
+                        for (int e = 0; e < EPV; e++) {
+                            if (!(f[e] < T_thr)) {
+                                const int pos = atomicAdd(&s_count, 1);
+                                if (pos < CAP)
+                                    s_cand[pos] = make_cand(order_key(f[e]),
+                                                            static_cast<uint32_t>((c_v0 + j * THREADS + tid) * EPV + e - head));
+                            }
                         }
                     }
                 }
@@ -318,7 +346,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                     const int i = (c_v0 + lv) * EPV + e - head;
                     if (lv < c_nvt && i >= 0 && i < cols) {
                         const int pos = atomicAdd(&s_count, 1);
-                        if (pos < kCandCap)
+                        if (pos < CAP)
                             s_cand[pos] = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
                     }
                 }
@@ -327,13 +355,25 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 
         if (c_last) {
             PROF_MARK(4);
-            // ================= end of a row part: statistics, publish =================
-            const uint32_t mkey = __reduce_max_sync(kFullMask, lane < NW ? s_wm[parity][lane] : 0u);
+            // ================= end of a row part: statistics, filter, publish =================
+            uint32_t mkey = order_key(m_t);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1)
+                mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
+            if (lane == 0)
+                s_wm[0][warp] = mkey;
+            __syncthreads();
+            mkey = lane < NW ? s_wm[0][lane] : 0u;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1)
+                mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
             const float mx = key_to_float(mkey);  // part maximum of the stored logits
             float s = (m_t == -INFINITY) ? 0.0f : s_t * ex2_approx((m_t - mx) * c1);
             s = warp_sum(s);
             if (lane == 0)
                 s_red[warp] = s;
+            if (tid == 0)
+                s_tmp[0] = 0;
             __syncthreads();
             const float S = warp_sum(lane < NW ? s_red[lane] : 0.0f);
             const float mz = __fmul_rn(mx, p.inv_t);
@@ -346,19 +386,17 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             const int nvalid = e1 > e0 ? e1 - e0 : 0;
             const int kk = nvalid < p.k ? nvalid : p.k;
 
-            if (C > kCandCap || (p.need_sum && S != S)) {
+            uint64_t *s_list = s_cand, *s_other = s_work;
+            if (C > CAP || (p.need_sum && S != S)) {
+                // more candidates than slots, or NaN in the part (NaN ranks first but is invisible to the
+                // thread maxima): exact radix select over the part, re-read from L2
                 __syncthreads();
                 const int fv1 = part_v1 < nvr ? part_v1 : nvr;
                 select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, &s_count, s_hist, s_pick);
                 C = s_count;
-            }
-            // Candidates pushed under the weaker thresholds of the early tiles are dropped now: at least
-            // k elements of this part reach the final threshold.
-            uint64_t *s_list = s_cand, *s_other = s_work;
-            if (tkey != 0u && C > p.k) {
-                if (tid == 0)
-                    s_tmp[0] = 0;
-                __syncthreads();
+            } else if (tkey != 0u && C > p.k) {
+                // Candidates pushed under the weaker thresholds of the early tiles are dropped now: at
+                // least k elements of this part reach the final threshold.
                 for (int i = tid; i < C; i += THREADS) {
                     const uint64_t c = s_cand[i];
                     if (cand_key(c) >= tkey)
@@ -368,84 +406,76 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                 C = s_tmp[0];
                 s_list = s_work;
                 s_other = s_cand;
-                __syncthreads();
             }
             PROF_MARK(5);
 
-            if (!waited) {  // first write to memory another launch may still be using
+            if (!waited) {  // first write to memory the previous call may still be using
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
             }
-            const bool whole_row = part_v0 == 0 && part_v1 == static_cast<int>(nvv);
-            if (whole_row) {
-                if (p.packets_out && tid == 0) {
-                    uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
-                    pk[0] = __float_as_uint(mz);
-                    pk[1] = __float_as_uint(S);
-                    pk[2] = static_cast<uint32_t>(kk);
-                    pk[3] = 0;
-                }
-                select_and_emit<T, THREADS>(p, c_row, s_list, C, s_other, mz, S, nullptr, s_tmp);
+            const uint32_t c_first = stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
+            const int pidx = static_cast<int>(blockIdx.x - c_first);
+            unsigned long long *mylist = p.lists + (static_cast<int64_t>(c_row) * p.splits + pidx) * lstride;
+            if (C > p.list_cap) {
+                // more than a part may publish: cut them down to the part's own k best
+                select_and_emit<T, THREADS>(p, c_row, s_list, C, s_other, 0.0f, 0.0f, mylist + 2, s_tmp);
+                C = kk;
             } else {
-                const uint32_t c_first = stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
-                const int pidx = static_cast<int>(blockIdx.x - c_first);
-                unsigned long long *mylist = p.lists + (static_cast<int64_t>(c_row) * p.splits + pidx) * lstride;
-                if (C > p.list_cap) {
-                    select_and_emit<T, THREADS>(p, c_row, s_list, C, s_other, 0.0f, 0.0f, mylist + 2, s_tmp);
-                    C = kk;
-                } else {
-                    for (int i = tid; i < C; i += THREADS)
-                        mylist[2 + i] = s_list[i];
-                }
-                if (tid == 0) {
-                    mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-                    mylist[1] = static_cast<unsigned long long>(C);
-                }
-                __syncthreads();
-                // One thread orders the CTA's writes (made visible to it by the barrier) before the row's
-                // progress counter; the others stream on.  The part that completes the row selects.
-                if (tid == 0) {
-                    __threadfence();
-                    const unsigned int len = static_cast<unsigned int>(part_v1 - part_v0);
-                    const unsigned int done = atomicAdd(&p.counters[c_row], len) + len;
-                    PROF_MARK(6);
-                    if (done == nvv) {
-                        p.counters[c_row] = 0;  // ready for the next launch
-                        __threadfence();
-                        s_merge_row = c_row;
-                    }
-                }
+                for (int i = tid; i < C; i += THREADS)
+                    mylist[2 + i] = s_list[i];
             }
+            if (tid == 0) {
+                mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
+                mylist[1] = static_cast<unsigned long long>(C);
+            }
+            PROF_MARK(6);
             if (has_next) {
                 // ---- reset for the next row part ----
-                // (every read of the candidate list and its count lies before a barrier above; the next
-                // pushes come after the next tile's barrier)
+                __syncthreads();  // every thread is done with the candidate list and its count
                 m_t = -INFINITY;
                 s_t = 0.0f;
                 tkey = 0;
+                T_thr = key_to_float(0u);
                 part_v0 = v0;
+                part_tile = 0;
                 nfullw = (nvt < THREADS ? nvt : THREADS) / 32;
-                r_sel = nfullw > 0 ? (p.k + nfullw - 1) / nfullw : 33;
-                if (tid == THREADS - 1)
+                gs = group_lanes(nfullw);
+                if (tid == 0)
                     s_count = 0;
             }
         }
-        parity ^= 1;
         if (!has_next)
             break;
     }
-    // a selection triggered by the CTA's last part
-    __syncthreads();
+}
+
+// Kernel 2: one CTA per row gathers the published parts of the row and selects.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) softmax_topk_row_select_kernel(const ChunkParams p, int stream_grid) {
+    extern __shared__ __align__(16) uint64_t s_buf[];
+    __shared__ float s_red[THREADS / 32];
+    __shared__ int s_int[8 + 1024];
+    __shared__ int s_tmp[2];
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the parts are complete and visible after this
+    const int row = blockIdx.x;
+    const uint32_t grid = static_cast<uint32_t>(stream_grid);
+    const uint32_t nvv = static_cast<uint32_t>(p.nvv);
+    const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
+    const uint32_t per = static_cast<uint32_t>(p.per_cta);
+    const uint32_t parts = static_cast<uint32_t>(p.parts_per_row);
+    const uint32_t cf = stream_owner(static_cast<uint32_t>(row) * nvv, grid, per, nvv, total, parts);
+    const uint32_t cl = stream_owner(static_cast<uint32_t>(row + 1) * nvv - 1, grid, per, nvv, total, parts);
+    const int64_t lstride = 2 + p.list_cap;
     PROF_MARK(7);
-    if (s_merge_row >= 0) {
-        const int mrow = s_merge_row;
-        const uint32_t cf = stream_owner(static_cast<uint32_t>(mrow) * nvv, grid, per, nvv, total, parts);
-        const uint32_t cl = stream_owner(static_cast<uint32_t>(mrow + 1) * nvv - 1, grid, per, nvv, total, parts);
-        merge_lists<T, THREADS>(p, mrow, p.lists + static_cast<int64_t>(mrow) * p.splits * lstride, lstride,
-                                static_cast<int>(cl - cf + 1), s_merge, s_red, s_int, s_tmp);
-        __syncthreads();
-        PROF_MARK(12);
-    }
+    merge_lists<T, THREADS>(p, row, p.lists + static_cast<int64_t>(row) * p.splits * lstride, lstride,
+                            static_cast<int>(cl - cf + 1), s_buf, s_red, s_int, s_tmp);
+    __syncthreads();
+    PROF_MARK(12);
+#ifdef VKOP_PHASE_PROF
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0)
+        atomicAdd(&g_phase_seq, 1);  // approximate: the last row's CTA closes the call
+#endif
 }
 
 // ---------------------------------------------------------------------------
@@ -456,10 +486,10 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     const int esz = d.dtype == VKOP_F32 ? 4 : 2;
     const int epv = 16 / esz;
     const int64_t stride = d.row_stride ? d.row_stride : d.cols;
-    // rows that all start on a 16-byte boundary (given an aligned base, checked at launch): exact slot count
+    // rows that all start on a 16-byte boundary: exact slot count and the cheaper address arithmetic
     const bool aligned = base_aligned && (stride * esz) % 16 == 0;
     const int64_t nvv = aligned ? (d.cols + epv - 1) / epv : (d.cols + 2 * (epv - 1)) / epv;
-    if (d.rows <= 0 || d.cols >= (1ll << 30) || d.rows * nvv >= (1ll << 32) - (1ll << 20))
+    if (d.rows <= 0 || d.rows >= (1ll << 31) || d.cols >= (1ll << 30) || d.rows * nvv >= (1ll << 32) - (1ll << 20))
         return VKOP_UNSUPPORTED;
     const int64_t total = d.rows * nvv;
     const int64_t slots = kNumSms * kStreamCtasPerSm;
@@ -480,8 +510,8 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     if (maxparts * d.k > kMergeMaxSlots || maxparts > 1024)
         return VKOP_UNSUPPORTED;
     int list_cap = static_cast<int>(kMergeMaxSlots / maxparts);
-    if (list_cap > kListCapMax)
-        list_cap = kListCapMax;
+    if (list_cap > kStreamListCap)
+        list_cap = kStreamListCap;
     plan->grid = static_cast<int>(grid);
     plan->per_cta = per;
     plan->nvv = nvv;
@@ -490,32 +520,42 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     plan->parts_per_row = parts_per_row;
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
-    plan->counters_bytes = ((static_cast<size_t>(d.rows) * 4 + 255) / 256) * 256;
+    plan->counters_bytes = 0;
     plan->lists_bytes = static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
-    plan->smem_bytes = (2 * static_cast<size_t>(kCandCap) + 2 * (static_cast<size_t>(maxparts) * list_cap + 32)) * 8;
+    plan->smem_bytes = 2 * static_cast<size_t>(kStreamThreads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamCandCap) * 8;
+    plan->select_smem_bytes = 2 * (static_cast<size_t>(maxparts) * list_cap + 32) * 8;
     return VKOP_OK;
 }
 
-template <typename T, bool ALIGNED>
-static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStream_t stream) {
-    auto kern = softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED>;
-    if (plan.smem_bytes > 32 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) !=
-            cudaSuccess)
+template <typename Kern, typename... Args>
+static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream, Args... args) {
+    if (smem > 32 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return VKOP_CUDA_ERROR;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
-    cfg.blockDim = dim3(kStreamThreads);
-    cfg.dynamicSmemBytes = plan.smem_bytes;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess)
-        return VKOP_CUDA_ERROR;
-    note_launch();
+    return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? VKOP_OK : VKOP_CUDA_ERROR;
+}
+
+template <typename T, bool ALIGNED>
+static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStream_t stream) {
+    int rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED>, static_cast<unsigned>(plan.grid),
+                        kStreamThreads, plan.smem_bytes, stream, p);
+    if (rc != VKOP_OK)
+        return rc;
+    rc = launch_pdl(softmax_topk_row_select_kernel<T, kSelectThreads>, static_cast<unsigned>(p.rows), kSelectThreads,
+                    plan.select_smem_bytes, stream, p, plan.grid);
+    if (rc != VKOP_OK)
+        return rc;
+    note_launch(2);
     return check_launch();
 }
 
@@ -540,8 +580,8 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.index_offset = d.index_offset;
     p.out_values = out_values;
     p.out_indices = out_indices;
-    p.counters = reinterpret_cast<unsigned int *>(workspace);
-    p.lists = reinterpret_cast<unsigned long long *>(static_cast<char *>(workspace) + plan.counters_bytes);
+    p.counters = nullptr;
+    p.lists = reinterpret_cast<unsigned long long *>(workspace);
     p.packets_out = reinterpret_cast<uint32_t *>(packets_out);
     p.nvv = plan.nvv;
     p.per_cta = plan.per_cta;
