@@ -66,5 +66,59 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(HERE, "libvkop_host.so")
+API_TEST = os.path.join(ROOT, "tests", "cpp", "op_api_test")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _stale(target: str, sources) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    for s in sources:
+        if os.path.isdir(s):
+            for root, _, files in os.walk(s):
+                if any(os.path.getmtime(os.path.join(root, f)) > t for f in files):
+                    return True
+        elif os.path.getmtime(s) > t:
+            return True
+    return False
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ operator API (host side) above the C ABI: libvkop_host.so, built with g++."""
+    build(force=False)
+    srcs = [os.path.join(HOST, "src", "runtime.cpp"), os.path.join(HOST, "src", "host_capi.cpp")]
+    deps = srcs + [os.path.join(HOST, "include"), os.path.join(ROOT, "include"), LIB]
+    if force or _stale(HOST_LIB, deps):
+        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-I", os.path.join(HOST, "include"),
+               "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA_HOME, "include"), *srcs, "-o", HOST_LIB + ".tmp",
+               "-L", HERE, "-lvkop_cuda", "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN"]
+        subprocess.run(cmd, check=True)
+        os.replace(HOST_LIB + ".tmp", HOST_LIB)
+    return HOST_LIB
+
+
+def build_api_test(force: bool = False) -> str:
+    """The C++ test program that drives the operator API against the oracle (test infrastructure)."""
+    build_host(force=False)
+    sys.path.insert(0, ROOT)
+    from oracle import build as oracle_build
+
+    oracle_lib = oracle_build.build()
+    src = os.path.join(ROOT, "tests", "cpp", "op_api_test.cpp")
+    if force or _stale(API_TEST, [src, HOST_LIB, oracle_lib, os.path.join(HOST, "include")]):
+        cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-I", os.path.join(HOST, "include"), "-I", os.path.join(ROOT, "include"),
+               "-I", os.path.join(CUDA_HOME, "include"), src, "-o", API_TEST + ".tmp", "-L", HERE, "-lvkop_host", "-lvkop_cuda",
+               "-L", os.path.dirname(oracle_lib), "-lvkop_oracle", "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart",
+               "-Wl,-rpath,$ORIGIN/../../vkop_b200:$ORIGIN/../../oracle"]
+        subprocess.run(cmd, check=True)
+        os.replace(API_TEST + ".tmp", API_TEST)
+    return API_TEST
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_host(force="--force" in sys.argv))
+    print(build_api_test(force="--force" in sys.argv))
