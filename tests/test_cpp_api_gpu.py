@@ -38,23 +38,16 @@ def test_host_pipeline_from_python():
     import oracle
     from vkop_b200 import workloads
 
-    lib = ctypes.CDLL(HOST_LIB)
-    lib.vkop_host_pipeline_create.restype = ctypes.c_void_p
-    lib.vkop_host_pipeline_create.argtypes = [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int]
-    lib.vkop_host_pipeline_run.argtypes = [ctypes.c_void_p] * 5
-    lib.vkop_host_pipeline_destroy.argtypes = [ctypes.c_void_p]
-    lib.vkop_host_last_error.restype = ctypes.c_char_p
+    from vkop_b200 import host_api
+
     x = workloads.llm_vocab(rows=8)
     xa = x.numpy()
-    for fuse in (1, 0):
-        h = lib.vkop_host_pipeline_create(0, 8, xa.shape[1], 0, 50, 1.0, fuse)
-        assert h, lib.vkop_host_last_error()
+    for fuse in (True, False):
+        pipe = host_api.HostPipeline(0, 8, xa.shape[1], 0, 50, 1.0, fuse)
         vals = np.empty((8, 50), np.float32)
         idx = np.empty((8, 50), np.int32)
-        ms = ctypes.c_double()
-        rc = lib.vkop_host_pipeline_run(h, xa.ctypes.data, vals.ctypes.data, idx.ctypes.data, ctypes.addressof(ms))
-        assert rc == 0, lib.vkop_host_last_error()
-        lib.vkop_host_pipeline_destroy(h)
+        assert pipe.run(xa, vals, idx) >= 0.0
+        pipe.close()
         wv, wi = oracle.softmax_topk(xa, 50)
         assert np.array_equal(idx, wi)
         assert np.all(np.abs(vals - wv) <= 1e-6 + 1e-5 * np.abs(wv))

@@ -32,21 +32,23 @@ struct ChunkParams {
     int64_t vstride;   // vectors between the starts of consecutive rows (rows 16-byte aligned only)
     int parts_per_row; // > 0: every row is cut into this many CTAs and no CTA crosses a row
     int input_ready;   // the logits were complete before this launch was enqueued
+#ifdef VKOP_PHASE_PROF
+    int prof_seq;      // development aid: sequence number of the call
+#endif
 };
 
 #ifdef VKOP_PHASE_PROF
 // Development aid, compiled only on request: per-CTA timestamps of the kernels' phases, for the last
 // eight launches (slot = launch sequence number modulo 8).
 static __device__ unsigned long long g_phase_prof[8 * 1024 * 16];
-static __device__ int g_phase_seq;
-__device__ __forceinline__ void prof_mark(int slot) {
+__device__ __forceinline__ void prof_mark(int seq, int slot) {
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_phase_prof[((g_phase_seq & 7) * 1024 + blockIdx.x) * 16 + slot] = t;
+        g_phase_prof[((seq & 7) * 1024 + blockIdx.x) * 16 + slot] = t;
     }
 }
-#define PROF_MARK(s) prof_mark(s)
+#define PROF_MARK(s) prof_mark(p.prof_seq, s)
 #else
 #define PROF_MARK(s)
 #endif

@@ -12,11 +12,15 @@
 // thread's own copy groups (no spin-wait anywhere).
 //
 // Per tile and thread: the maximum of its elements updates a running maximum
-// m_t and rescales a running exp-sum s_t (online softmax); the r-th largest
-// running thread maximum of each warp, minimised over the warps, refreshes the
-// selection threshold T (one barrier per tile), which only rises while the CTA
-// stays in one row; elements >= T are appended to a candidate list in shared
-// memory.  Early tiles pass a hundred candidates, later ones a handful.
+// m_t and rescales a running exp-sum s_t (online softmax).  The running thread
+// maxima give the selection threshold T: lanes form groups so that there are
+// at least k groups, and T is the smallest group maximum, so at least k
+// elements of the part reach T.  T is refreshed on tiles 0, 1, 3, 7, ... of a
+// part (one barrier each; it settles quickly and only rises inside a part).
+// An element >= T is kept: every thread owns a few private slots in shared
+// memory and appends there with a plain predicated store -- no atomic and no
+// divergent path on the common route; a thread whose slots are full appends
+// to a small shared overflow list instead.
 //
 // When a CTA leaves a row (or its range ends) it finishes that row part: the
 // statistics are reduced over the CTA, candidates below the final threshold
@@ -45,7 +49,8 @@ constexpr int kStreamVecs = 4;
 constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
 constexpr int kUnit = 256;            // range boundaries inside a row are multiples of this many vectors
-constexpr int kStreamCandCap = 2048;  // candidate slots of one row part
+constexpr int kStreamCandCap = 2048;  // candidate slots of one row part (= threads x private slots)
+constexpr int kStreamSlots = kStreamCandCap / kStreamThreads;  // private candidate slots of one thread
 constexpr int kStreamListCap = 512;   // most candidates one row part publishes
 constexpr int kSelectThreads = 256;
 
@@ -100,8 +105,14 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     constexpr int CAP = kStreamCandCap;
     extern __shared__ __align__(16) uint64_t s_dyn[];
     uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);  // two tile stages of TV vectors
-    uint64_t *s_cand = s_dyn + 2 * TV * 2;              // candidates of the current row part: CAP slots
-    uint64_t *s_work = s_cand + CAP;                    // second region: filtered list / in-CTA selection
+    // First region: while a part streams, SLOTS private slots per thread (slot s of thread t at
+    // s * THREADS + t), each (float bits << 32 | index in the row); after the part, the dense list.
+    uint64_t *s_cand = s_dyn + 2 * TV * 2;
+    // Second region: while a part streams, the overflow list of threads whose slots are full
+    // (s_count entries); after the part, scratch of the in-CTA selection.
+    uint64_t *s_work = s_cand + CAP;
+    constexpr int SLOTS = CAP / THREADS;
+    static_assert(SLOTS * THREADS == CAP && SLOTS >= 1, "private slots tile the first region");
     __shared__ uint32_t s_wr[2][NW], s_wm[2][NW];
     __shared__ float s_red[NW];
     __shared__ int s_hist[256];
@@ -195,6 +206,20 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     int nfullw = (nvt < THREADS ? nvt : THREADS) / 32;  // warps whose threads all own data in this part
     int gs = group_lanes(nfullw);
     int parity = 0;
+    uint64_t *slot = s_cand + tid;  // this thread's next private slot; past slot_end the slots are full
+    uint64_t *const slot_end = s_cand + CAP;
+    // Keeps one element of the part: idx is its index in the row.
+    auto keep = [&](float fv, int idx) {
+        const uint64_t ent = (static_cast<uint64_t>(__float_as_uint(fv)) << 32) | static_cast<uint32_t>(idx);
+        if (slot < slot_end) {
+            *slot = ent;
+        } else {
+            const int pos = atomicAdd(&s_count, 1);
+            if (pos < CAP)
+                s_work[pos] = ent;
+        }
+        slot += THREADS;
+    };
     if (tid == 0)
         s_count = 0;
     __syncthreads();
@@ -317,21 +342,16 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         // ---- candidates of this tile ----
         if (!allpass) {
             // padding is -inf and T is above -inf: whatever passes is a valid element
-            if (!(vm < T_thr)) {
+            const int ibase = (c_v0 + tid) * EPV - head;
 #pragma unroll
-                for (int j = 0; j < VECS; j++) {
-                    if (!(vmax[j] < T_thr)) {
-                        float f[EPV];
-                        Elem<T>::unpack(d[j], f);
+            for (int j = 0; j < VECS; j++) {
+                if (!(vmax[j] < T_thr)) {
+                    float f[EPV];
+                    Elem<T>::unpack(d[j], f);
 #pragma unroll
-                        for (int e = 0; e < EPV; e++) {
-                            if (!(f[e] < T_thr)) {
-                                const int pos = atomicAdd(&s_count, 1);
-                                if (pos < CAP)
-                                    s_cand[pos] = make_cand(order_key(f[e]),
-                                                            static_cast<uint32_t>((c_v0 + j * THREADS + tid) * EPV + e - head));
-                            }
-                        }
+                    for (int e = 0; e < EPV; e++) {
+                        if (!(f[e] < T_thr))
+                            keep(f[e], ibase + j * THREADS * EPV + e);
                     }
                 }
             }
@@ -344,11 +364,8 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 #pragma unroll
                 for (int e = 0; e < EPV; e++) {
                     const int i = (c_v0 + lv) * EPV + e - head;
-                    if (lv < c_nvt && i >= 0 && i < cols) {
-                        const int pos = atomicAdd(&s_count, 1);
-                        if (pos < CAP)
-                            s_cand[pos] = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
-                    }
+                    if (lv < c_nvt && i >= 0 && i < cols)
+                        keep(f[e], i);
                 }
             }
         }
@@ -377,7 +394,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             __syncthreads();
             const float S = warp_sum(lane < NW ? s_red[lane] : 0.0f);
             const float mz = __fmul_rn(mx, p.inv_t);
-            int C = s_count;
+            const int novf = s_count;  // entries of the overflow list
 
             const int part_v1 = c_v0 + c_nvt;
             int e0 = part_v0 * EPV - head, e1 = part_v1 * EPV - head;
@@ -386,26 +403,40 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             const int nvalid = e1 > e0 ? e1 - e0 : 0;
             const int kk = nvalid < p.k ? nvalid : p.k;
 
+            // Private slots and overflow list -> one dense list of candidates (key << 32 | ~index) in the
+            // first region.  Entries kept under the weaker thresholds of the early tiles are dropped: at
+            // least k elements of this part reach the final threshold.  (No threshold: tkey is 0, all stay.)
+            uint64_t mine[SLOTS];
+            const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
+#pragma unroll
+            for (int q = 0; q < SLOTS; q++)
+                mine[q] = q < held ? s_cand[q * THREADS + tid] : 0ull;
+            __syncthreads();  // every private slot has been read: the region is free for the list
+            auto to_list = [&](uint64_t ent) {
+                const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
+                if (key >= tkey) {
+                    const int pos = atomicAdd(&s_tmp[0], 1);
+                    if (pos < CAP)
+                        s_cand[pos] = make_cand(key, static_cast<uint32_t>(ent));
+                }
+            };
+#pragma unroll
+            for (int q = 0; q < SLOTS; q++) {
+                if (q < held)
+                    to_list(mine[q]);
+            }
+            for (int i = tid; i < (novf < CAP ? novf : CAP); i += THREADS)
+                to_list(s_work[i]);
+            __syncthreads();
+            int C = s_tmp[0];
+
             uint64_t *s_list = s_cand, *s_other = s_work;
-            if (C > CAP || (p.need_sum && S != S)) {
+            if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
                 // more candidates than slots, or NaN in the part (NaN ranks first but is invisible to the
                 // thread maxima): exact radix select over the part, re-read from L2
-                __syncthreads();
                 const int fv1 = part_v1 < nvr ? part_v1 : nvr;
                 select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, &s_count, s_hist, s_pick);
                 C = s_count;
-            } else if (tkey != 0u && C > p.k) {
-                // Candidates pushed under the weaker thresholds of the early tiles are dropped now: at
-                // least k elements of this part reach the final threshold.
-                for (int i = tid; i < C; i += THREADS) {
-                    const uint64_t c = s_cand[i];
-                    if (cand_key(c) >= tkey)
-                        s_work[atomicAdd(&s_tmp[0], 1)] = c;
-                }
-                __syncthreads();
-                C = s_tmp[0];
-                s_list = s_work;
-                s_other = s_cand;
             }
             PROF_MARK(5);
 
@@ -440,6 +471,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                 part_tile = 0;
                 nfullw = (nvt < THREADS ? nvt : THREADS) / 32;
                 gs = group_lanes(nfullw);
+                slot = s_cand + tid;
                 if (tid == 0)
                     s_count = 0;
             }
@@ -472,10 +504,6 @@ __global__ void __launch_bounds__(THREADS) softmax_topk_row_select_kernel(const 
                             static_cast<int>(cl - cf + 1), s_buf, s_red, s_int, s_tmp);
     __syncthreads();
     PROF_MARK(12);
-#ifdef VKOP_PHASE_PROF
-    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0)
-        atomicAdd(&g_phase_seq, 1);  // approximate: the last row's CTA closes the call
-#endif
 }
 
 // ---------------------------------------------------------------------------
@@ -588,6 +616,10 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.vstride = plan.vstride;
     p.parts_per_row = plan.parts_per_row;
     p.input_ready = (d.flags & VKOP_FLAG_INPUT_READY) ? 1 : 0;
+#ifdef VKOP_PHASE_PROF
+    static int prof_calls = 0;
+    p.prof_seq = prof_calls++;
+#endif
     if (plan.aligned && reinterpret_cast<uintptr_t>(logits) % 16 != 0)
         return VKOP_INVALID_ARG;  // planned for an aligned base
 #define VKOP_STREAM(T) (plan.aligned ? launch_stream_t<T, true>(p, plan, stream) : launch_stream_t<T, false>(p, plan, stream))
