@@ -30,7 +30,7 @@ struct StreamPlan {
     int grid;
     int64_t per_cta, nvv, vstride;
     int maxparts, list_cap, parts_per_row, aligned;
-    size_t counters_bytes, lists_bytes, smem_bytes, select_smem_bytes;
+    size_t counters_bytes, lists_bytes, smem_bytes;
 };
 // base_aligned: the logits pointer is a multiple of 16 (rows then are too when the row stride is)
 int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *plan);

@@ -32,6 +32,7 @@ struct ChunkParams {
     int64_t vstride;   // vectors between the starts of consecutive rows (rows 16-byte aligned only)
     int parts_per_row; // > 0: every row is cut into this many CTAs and no CTA crosses a row
     int input_ready;   // the logits were complete before this launch was enqueued
+    unsigned long long *arrivals;  // CTAs that ever started on this workspace (gives every call its number)
 #ifdef VKOP_PHASE_PROF
     int prof_seq;      // development aid: sequence number of the call
 #endif
@@ -277,18 +278,23 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
 // Gathers the candidate lists of the G parts of one row into shared memory,
 // merges their statistics and selects.  Executed by one whole CTA.
 // lists: G blocks of `stride` 64-bit words: header word 0 = (m, s) as float
-// bits, header word 1 = count; then the candidates.
+// bits; header word 1 = count in bits 0-15, then 32 bits of threshold key (at
+// least k of the part's candidates reach it; 0 = none) and 16 bits the
+// streaming kernel keeps for its slot state; then the candidates.
+// s_buf holds the gathered candidates; s_sel is the scratch of the selection
+// (as many slots again), or null to take it right behind the candidates.
 template <typename T, int THREADS>
 __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned long long *lists, int64_t stride, int G,
-                            uint64_t *s_buf, float *s_red, int *s_int, int *s_tmp) {
+                            uint64_t *s_buf, uint64_t *s_sel, float *s_red, int *s_int, int *s_tmp) {
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float M, S;
     int n;
     if (G <= NW && p.list_cap <= 512) {
         // Few, short lists: warp g takes list g and fetches its header and its whole capacity in one
-        // round trip (entries past the count are ignored); one barrier later every warp knows all counts
-        // and drops its entries at the right offset.
+        // round trip (entries past the count are ignored).  One barrier later every warp knows all
+        // headers: the largest of the parts' thresholds bounds the row's k-th best from below (that
+        // part alone holds k candidates at or above it), so only candidates that reach it are kept.
         const int g = warp;
         unsigned long long regs[16];
         int cnt = 0;
@@ -300,23 +306,22 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
                 const int i = lane + 32 * j;
                 regs[j] = i < p.list_cap ? __ldcg(L + 2 + i) : 0ull;
             }
-            cnt = static_cast<int>(h1);
+            cnt = static_cast<int>(h1 & 0xFFFFu);
             if (lane == 0) {
-                s_int[8 + g] = cnt;
+                s_int[8 + g] = static_cast<int>(static_cast<uint32_t>(h1 >> 16));       // threshold key of the part
                 s_int[8 + NW + g] = static_cast<int>(static_cast<uint32_t>(h0));         // max z bits
                 s_int[8 + 2 * NW + g] = static_cast<int>(static_cast<uint32_t>(h0 >> 32));  // sum bits
             }
         }
+        if (tid == 0)
+            s_tmp[0] = 0;
         __syncthreads();
         PROF_MARK(8);
-        int off = 0;
-        n = 0;
+        uint32_t trow = 0;
         M = -INFINITY;
         for (int q = 0; q < G; q++) {
-            const int c = s_int[8 + q];
-            if (q < g)
-                off += c;
-            n += c;
+            const uint32_t tq = static_cast<uint32_t>(s_int[8 + q]);
+            trow = tq > trow ? tq : trow;
             M = fmaxf(M, __int_as_float(s_int[8 + NW + q]));
         }
         S = 0.0f;
@@ -329,11 +334,21 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const int i = lane + 32 * j;
-                if (i < cnt)
-                    s_buf[off + i] = regs[j];
+                const bool pass = i < cnt && cand_key(regs[j]) >= trow;
+                const unsigned b = __ballot_sync(kFullMask, pass);
+                if (b != 0u) {
+                    int base = 0;
+                    if (lane == 0)
+                        base = atomicAdd(&s_tmp[0], __popc(b));
+                    base = __shfl_sync(kFullMask, base, 0);
+                    if (pass)
+                        s_buf[base + __popc(b & ((1u << lane) - 1u))] = regs[j];
+                }
             }
         }
         __syncthreads();
+        n = s_tmp[0];
+        __syncthreads();  // s_tmp is reused by the selection
         PROF_MARK(9);
     } else {
         // statistics and list offsets (one warp walks the headers)
@@ -353,7 +368,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
                     const float sg = __uint_as_float(static_cast<uint32_t>(h >> 32));
                     if (sg != 0.0f)  // an all -inf part has sum 0 and no defined maximum
                         s += sg * expf(mg - m);
-                    cnt = static_cast<int>(__ldcg(lists + g * stride + 1));
+                    cnt = static_cast<int>(__ldcg(lists + g * stride + 1) & 0xFFFFu);
                 }
                 int incl = cnt;
 #pragma unroll
@@ -397,7 +412,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
         pk[2] = static_cast<uint32_t>(nsel);
         pk[3] = 0;
     }
-    select_and_emit<T, THREADS>(p, row, s_buf, n, s_buf + ((n + 31) & ~31), M, S, nullptr, s_tmp);
+    select_and_emit<T, THREADS>(p, row, s_buf, n, s_sel ? s_sel : s_buf + ((n + 31) & ~31), M, S, nullptr, s_tmp);
 }
 
 }  // namespace vkop_cuda

@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
     __threadfence();
     if (tid == 0)
         p.counters[row] = 0;  // ready for the next launch
-    merge_lists<T, THREADS>(p, row, p.lists + row * p.splits * lstride, lstride, p.splits, s_cand, s_red, s_int, s_tmp);
+    merge_lists<T, THREADS>(p, row, p.lists + row * p.splits * lstride, lstride, p.splits, s_cand, nullptr, s_red, s_int, s_tmp);
     __syncthreads();
     PROF_MARK(6);
 }

@@ -50,9 +50,7 @@ constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
 constexpr int kUnit = 256;            // range boundaries inside a row are multiples of this many vectors
 constexpr int kStreamCandCap = 2048;  // candidate slots of one row part (= threads x private slots)
-constexpr int kStreamSlots = kStreamCandCap / kStreamThreads;  // private candidate slots of one thread
 constexpr int kStreamListCap = 512;   // most candidates one row part publishes
-constexpr int kSelectThreads = 256;
 
 // Snaps a slot offset inside a row to the nearest allowed boundary.
 __host__ __device__ inline uint32_t snap_in_row(uint32_t v, uint32_t nvv) {
@@ -114,15 +112,30 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     constexpr int SLOTS = CAP / THREADS;
     static_assert(SLOTS * THREADS == CAP && SLOTS >= 1, "private slots tile the first region");
     __shared__ uint32_t s_wr[2][NW], s_wm[2][NW];
+    __shared__ __align__(16) int s_thist[2][256];  // histograms of thread maxima (threshold refresh), used in turn
     __shared__ float s_red[NW];
     __shared__ int s_hist[256];
     __shared__ int s_pick[4];
     __shared__ int s_tmp[2];
+    __shared__ int s_int[8 + 1024];
     __shared__ int s_count;
+    __shared__ uint32_t s_epoch, s_tnew;
+    __shared__ int s_flag[2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t grid = gridDim.x;
+    // The number of this call on its workspace: CTAs draw arrival tickets, and the next call is let
+    // in only after every CTA of this one has drawn (the barrier orders the draw before the signal),
+    // so the tickets of one call are one block of `grid` consecutive numbers.
+    if (tid == 0)
+        s_epoch = static_cast<uint32_t>(atomicAdd(p.arrivals, 1ull) / grid);
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Calls alternate between two sets of scratch lists and arrival counters, so a call never has to
+    // wait for the row merges of the call right before it, only for those of the call before that.
+    const uint32_t epoch = s_epoch;
+    const int64_t set = epoch & 1u;
+    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
     const uint32_t nvv = static_cast<uint32_t>(p.nvv);
     const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
     const uint32_t per = static_cast<uint32_t>(p.per_cta);
@@ -206,6 +219,11 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     int nfullw = (nvt < THREADS ? nvt : THREADS) / 32;  // warps whose threads all own data in this part
     int gs = group_lanes(nfullw);
     int parity = 0;
+    // groups for the upper end of the histogram range: the smallest of their maxima should rank
+    // well inside the best k thread maxima
+    const int hgroups = p.k < 4 ? 1 : p.k < 10 ? 2 : p.k < 24 ? 4 : p.k < 56 ? 8 : 16;
+    if (tid < 256)
+        s_thist[0][tid] = 0;
     uint64_t *slot = s_cand + tid;  // this thread's next private slot; past slot_end the slots are full
     uint64_t *const slot_end = s_cand + CAP;
     // Keeps one element of the part: idx is its index in the row.
@@ -313,25 +331,82 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
 
         // ---- threshold refresh from the running thread maxima: on tiles 0, 1, 3, 7, ... of the part and
-        // on its last tile (the threshold settles quickly); the other tiles need no barrier at all ----
+        // on its last tile (the threshold settles quickly); the other tiles need no barrier at all.
+        // Any T that at least k thread maxima reach is a valid bound, since they are k different
+        // elements of the part.  First a coarse pair: lo, the smallest maximum over at least k groups of
+        // lanes (valid, but several times too many elements reach it), and hi, the smallest maximum
+        // over a few large groups (usually above the k-th largest).  Then a histogram of the thread
+        // maxima between lo and hi, 256 bins, picks the highest bin edge that k maxima still reach. ----
         if ((part_tile & (part_tile + 1)) == 0 || c_last) {
-            uint32_t key = order_key(m_t);
+            const uint32_t key = order_key(m_t);
+            uint32_t glo = key;
             if (gs > 0 && warp < nfullw) {
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t other = __shfl_xor_sync(kFullMask, key, o);
-                    key = o < gs ? max(key, other) : min(key, other);  // maximum inside a group, minimum over groups
+                    const uint32_t other = __shfl_xor_sync(kFullMask, glo, o);
+                    glo = o < gs ? max(glo, other) : min(glo, other);  // maximum inside a group, minimum over groups
                 }
             } else {
-                key = gs > 0 ? 0xFFFFFFFFu : 0u;  // a partly filled warp does not constrain the threshold
+                glo = gs > 0 ? 0xFFFFFFFFu : 0u;  // a partly filled warp does not constrain the threshold
             }
-            if (lane == 0)
-                s_wr[parity][warp] = key;
+            const uint32_t wmax = __reduce_max_sync(kFullMask, key);
+            if (lane == 0) {
+                s_wr[parity][warp] = glo;
+                s_wm[parity][warp] = wmax;
+            }
             __syncthreads();
-            uint32_t t_new = lane < NW ? s_wr[parity][lane] : 0xFFFFFFFFu;
+            if (tid < 256)
+                s_thist[parity ^ 1][tid] = 0;  // the histogram of the refresh after this one (everybody is done with it)
+            uint32_t lo = lane < NW ? s_wr[parity][lane] : 0xFFFFFFFFu;
+            lo = __reduce_min_sync(kFullMask, lo);
+            // hi: warps are paired up into hgroups groups; the smallest group maximum
+            uint32_t hi = 0xFFFFFFFFu;
+            if (lane < hgroups) {
+                hi = 0u;
+                for (int w = lane; w < NW; w += hgroups)
+                    hi = max(hi, s_wm[parity][w]);
+            }
+            hi = __reduce_min_sync(kFullMask, hi);
+            uint32_t t_new = lo;
+            if (lo != 0u && hi > lo) {  // (the same for every thread of the CTA)
+                const uint32_t range = hi - lo;
+                const int shift = range > 255u ? 24 - __clz(range) : 0;  // range >> shift <= 255
+                if (key >= lo) {
+                    const uint32_t b = (key - lo) >> shift;
+                    atomicAdd(&s_thist[parity][b < 255u ? b : 255u], 1);
+                }
+                __syncthreads();
+                if (warp == 0) {
+                    // lane l owns bins 8l .. 8l+7; suffix counts over the lanes, then inside the lane that crosses k
+                    const int4 h0 = *reinterpret_cast<const int4 *>(&s_thist[parity][8 * lane]);
+                    const int4 h1 = *reinterpret_cast<const int4 *>(&s_thist[parity][8 * lane + 4]);
+                    const int own = h0.x + h0.y + h0.z + h0.w + h1.x + h1.y + h1.z + h1.w;
+                    int suf = own;  // maxima in the bins of this lane and of the lanes above
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1)
-                t_new = min(t_new, __shfl_xor_sync(kFullMask, t_new, o));
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int v = __shfl_down_sync(kFullMask, suf, o);
+                        if (lane + o < 32)
+                            suf += v;
+                    }
+                    const unsigned reach = __ballot_sync(kFullMask, suf >= p.k);  // lane 0 always does: lo is valid
+                    if (lane == 31 - __clz(reach)) {
+                        const int c[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+                        int acc = suf - own, bin = 8 * lane;
+                        bool found = false;
+#pragma unroll
+                        for (int q = 7; q >= 0; q--) {
+                            acc += c[q];
+                            if (!found && acc >= p.k) {
+                                found = true;
+                                bin = 8 * lane + q;
+                            }
+                        }
+                        s_tnew = lo + (static_cast<uint32_t>(bin) << shift);
+                    }
+                }
+                __syncthreads();
+                t_new = s_tnew;
+            }
             tkey = t_new > tkey ? t_new : tkey;
             T_thr = key_to_float(tkey);
             parity ^= 1;
@@ -372,27 +447,44 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 
         if (c_last) {
             PROF_MARK(4);
-            // ================= end of a row part: statistics, filter, publish =================
-            uint32_t mkey = order_key(m_t);
+            // ================= end of a row part: statistics, publish, maybe merge the row =================
+            const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
+                                               : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
+            const int pidx = static_cast<int>(blockIdx.x - c_first);
+            unsigned long long *rowlists = p.lists + (set * p.rows + c_row) * p.splits * lstride;
+            unsigned long long *mylist = rowlists + pidx * lstride;
+            // This set of lists last served the call before the previous one: is that call's merge of
+            // this row finished?  (Asked early, used after the reduction below.)
+            unsigned int done_calls = 0;
+            if (tid == 0 && !waited)
+                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(done_calls) : "l"(row_done + c_row) : "memory");
+
+            // ---- statistics: per warp first, one barrier, then over the warps ----
+            uint32_t wkey = order_key(m_t);
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1)
-                mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
-            if (lane == 0)
-                s_wm[0][warp] = mkey;
+                wkey = max(wkey, __shfl_xor_sync(kFullMask, wkey, o));
+            {
+                const float mw = key_to_float(wkey);
+                const float sw = warp_sum(m_t == -INFINITY ? 0.0f : s_t * ex2_approx((m_t - mw) * c1));
+                if (lane == 0) {
+                    s_wm[0][warp] = wkey;
+                    s_red[warp] = sw;
+                }
+            }
+            if (tid == 0) {
+                s_tmp[0] = 0;
+                s_flag[0] = static_cast<int>(done_calls - epoch + 1u) >= 0;  // calls 0 .. epoch - 2 are done
+            }
             __syncthreads();
-            mkey = lane < NW ? s_wm[0][lane] : 0u;
+            uint32_t mkey = lane < NW ? s_wm[0][lane] : 0u;
+            const float mw = key_to_float(mkey);
+            const float sw = lane < NW ? s_red[lane] : 0.0f;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1)
                 mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
             const float mx = key_to_float(mkey);  // part maximum of the stored logits
-            float s = (m_t == -INFINITY) ? 0.0f : s_t * ex2_approx((m_t - mx) * c1);
-            s = warp_sum(s);
-            if (lane == 0)
-                s_red[warp] = s;
-            if (tid == 0)
-                s_tmp[0] = 0;
-            __syncthreads();
-            const float S = warp_sum(lane < NW ? s_red[lane] : 0.0f);
+            const float S = warp_sum(sw != 0.0f ? sw * ex2_approx((mw - mx) * c1) : sw);  // (a NaN sum stays NaN)
             const float mz = __fmul_rn(mx, p.inv_t);
             const int novf = s_count;  // entries of the overflow list
 
@@ -403,66 +495,139 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             const int nvalid = e1 > e0 ? e1 - e0 : 0;
             const int kk = nvalid < p.k ? nvalid : p.k;
 
-            // Private slots and overflow list -> one dense list of candidates (key << 32 | ~index) in the
-            // first region.  Entries kept under the weaker thresholds of the early tiles are dropped: at
-            // least k elements of this part reach the final threshold.  (No threshold: tkey is 0, all stay.)
-            uint64_t mine[SLOTS];
-            const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
-#pragma unroll
-            for (int q = 0; q < SLOTS; q++)
-                mine[q] = q < held ? s_cand[q * THREADS + tid] : 0ull;
-            __syncthreads();  // every private slot has been read: the region is free for the list
-            auto to_list = [&](uint64_t ent) {
-                const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
-                if (key >= tkey) {
-                    const int pos = atomicAdd(&s_tmp[0], 1);
-                    if (pos < CAP)
-                        s_cand[pos] = make_cand(key, static_cast<uint32_t>(ent));
-                }
-            };
-#pragma unroll
-            for (int q = 0; q < SLOTS; q++) {
-                if (q < held)
-                    to_list(mine[q]);
-            }
-            for (int i = tid; i < (novf < CAP ? novf : CAP); i += THREADS)
-                to_list(s_work[i]);
-            __syncthreads();
-            int C = s_tmp[0];
-
-            uint64_t *s_list = s_cand, *s_other = s_work;
-            if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
-                // more candidates than slots, or NaN in the part (NaN ranks first but is invisible to the
-                // thread maxima): exact radix select over the part, re-read from L2
-                const int fv1 = part_v1 < nvr ? part_v1 : nvr;
-                select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, &s_count, s_hist, s_pick);
-                C = s_count;
-            }
-            PROF_MARK(5);
-
-            if (!waited) {  // first write to memory the previous call may still be using
+            // Rare: the row's lists may still be in use.  Waiting for the whole previous call is always
+            // enough (it has merged this row only after the call before it had).
+            if (!waited && !s_flag[0]) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
             }
-            const uint32_t c_first = stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
-            const int pidx = static_cast<int>(blockIdx.x - c_first);
-            unsigned long long *mylist = p.lists + (static_cast<int64_t>(c_row) * p.splits + pidx) * lstride;
-            if (C > p.list_cap) {
-                // more than a part may publish: cut them down to the part's own k best
-                select_and_emit<T, THREADS>(p, c_row, s_list, C, s_other, 0.0f, 0.0f, mylist + 2, s_tmp);
-                C = kk;
+
+            // ---- candidates: private slots -> the part's list in scratch memory ----
+            // Entries kept under the weaker thresholds of the early tiles are dropped: at least k elements
+            // of this part reach the final threshold.  (No threshold: tkey is 0 and every entry stays.)
+            const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
+            uint32_t tpub = tkey;  // threshold the row merge may rely on
+            int C;
+            const bool plain = novf == 0 && !(p.need_sum && S != S);
+            if (plain) {
+#pragma unroll
+                for (int q = 0; q < SLOTS; q++) {
+                    uint64_t ent = 0;
+                    if (q < held)
+                        ent = s_cand[q * THREADS + tid];
+                    const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
+                    const bool pass = q < held && key >= tkey;
+                    const unsigned b = __ballot_sync(kFullMask, pass);
+                    if (b != 0u) {
+                        int base = 0;
+                        if (lane == 0)
+                            base = atomicAdd(&s_tmp[0], __popc(b));
+                        base = __shfl_sync(kFullMask, base, 0);
+                        const int pos = base + __popc(b & ((1u << lane) - 1u));
+                        if (pass && pos < p.list_cap)
+                            mylist[2 + pos] = make_cand(key, static_cast<uint32_t>(ent));
+                    }
+                }
+                __syncthreads();
+                C = s_tmp[0];
             } else {
-                for (int i = tid; i < C; i += THREADS)
-                    mylist[2 + i] = s_list[i];
+                C = p.list_cap + 1;
             }
+            if (C > p.list_cap) {
+                // Rare: more candidates than a part may publish, threads that ran out of private slots,
+                // or NaN in the part (NaN ranks first but is invisible to the thread maxima).  Everything
+                // goes to one dense list in shared memory and the part's own k best are selected.
+                __syncthreads();
+                uint64_t mine[SLOTS];
+#pragma unroll
+                for (int q = 0; q < SLOTS; q++)
+                    mine[q] = q < held ? s_cand[q * THREADS + tid] : 0ull;
+                if (tid == 0)
+                    s_tmp[0] = 0;
+                __syncthreads();  // every private slot has been read: the region is free for the list
+                auto to_list = [&](uint64_t ent) {
+                    const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
+                    if (key >= tkey) {
+                        const int pos = atomicAdd(&s_tmp[0], 1);
+                        if (pos < CAP)
+                            s_cand[pos] = make_cand(key, static_cast<uint32_t>(ent));
+                    }
+                };
+#pragma unroll
+                for (int q = 0; q < SLOTS; q++) {
+                    if (q < held)
+                        to_list(mine[q]);
+                }
+                for (int i = tid; i < (novf < CAP ? novf : CAP); i += THREADS)
+                    to_list(s_work[i]);
+                __syncthreads();
+                C = s_tmp[0];
+                if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
+                    // exact radix select over the part, re-read from L2
+                    const int fv1 = part_v1 < nvr ? part_v1 : nvr;
+                    select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, &s_count, s_hist, s_pick);
+                    C = s_count;
+                }
+                if (C > p.list_cap) {
+                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
+                    C = kk;
+                } else {
+                    for (int i = tid; i < C; i += THREADS)
+                        mylist[2 + i] = s_cand[i];
+                }
+                tpub = 0;  // the list holds the part's best, not everything above a threshold
+                __syncthreads();
+            }
+            PROF_MARK(5);
+
+            // ---- announce the part; the last part of a row to arrive merges the row ----
             if (tid == 0) {
                 mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-                mylist[1] = static_cast<unsigned long long>(C);
+                mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
+                const uint32_t c_end = parts > 0 ? c_first + parts - 1
+                                                 : stream_owner(static_cast<uint32_t>(c_row + 1) * nvv - 1, grid, per, nvv, total, parts);
+                const int nparts = static_cast<int>(c_end - c_first + 1);
+                // release: the list (written by all threads before the barrier) and the header; acquire:
+                // the lists of the parts that arrived earlier
+                unsigned int arrived;
+                unsigned int *ticket = p.counters + set * p.rows + c_row;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
+                const bool last = arrived == static_cast<unsigned int>(nparts - 1);
+                int in_order = 1;
+                if (last) {
+                    *ticket = 0;  // ready for the next call that uses this set
+                    // results of one row are written in call order: has the previous call written its own?
+                    unsigned int d;
+                    asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(row_done + c_row) : "memory");
+                    in_order = d == epoch;
+                }
+                s_flag[1] = last ? nparts : 0;
+                s_flag[0] = in_order;
             }
+            __syncthreads();
             PROF_MARK(6);
+            const int nparts = s_flag[1];
+            if (nparts > 0) {
+                PROF_MARK(7);
+                if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    waited = true;
+                }
+                // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
+                // in flight), the two candidate regions serve the selection: kMergeMaxSlots slots each
+                uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
+                merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
+                __syncthreads();
+                // the row's result is written and its lists are read
+                if (tid == 0) {
+                    const unsigned int d = epoch + 1u;
+                    asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+                }
+                PROF_MARK(12);
+            }
             if (has_next) {
                 // ---- reset for the next row part ----
-                __syncthreads();  // every thread is done with the candidate list and its count
+                __syncthreads();  // every thread is done with the candidate regions and the counters
                 m_t = -INFINITY;
                 s_t = 0.0f;
                 tkey = 0;
@@ -479,31 +644,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         if (!has_next)
             break;
     }
-}
-
-// Kernel 2: one CTA per row gathers the published parts of the row and selects.
-template <typename T, int THREADS>
-__global__ void __launch_bounds__(THREADS) softmax_topk_row_select_kernel(const ChunkParams p, int stream_grid) {
-    extern __shared__ __align__(16) uint64_t s_buf[];
-    __shared__ float s_red[THREADS / 32];
-    __shared__ int s_int[8 + 1024];
-    __shared__ int s_tmp[2];
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the parts are complete and visible after this
-    const int row = blockIdx.x;
-    const uint32_t grid = static_cast<uint32_t>(stream_grid);
-    const uint32_t nvv = static_cast<uint32_t>(p.nvv);
-    const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
-    const uint32_t per = static_cast<uint32_t>(p.per_cta);
-    const uint32_t parts = static_cast<uint32_t>(p.parts_per_row);
-    const uint32_t cf = stream_owner(static_cast<uint32_t>(row) * nvv, grid, per, nvv, total, parts);
-    const uint32_t cl = stream_owner(static_cast<uint32_t>(row + 1) * nvv - 1, grid, per, nvv, total, parts);
-    const int64_t lstride = 2 + p.list_cap;
-    PROF_MARK(7);
-    merge_lists<T, THREADS>(p, row, p.lists + static_cast<int64_t>(row) * p.splits * lstride, lstride,
-                            static_cast<int>(cl - cf + 1), s_buf, s_red, s_int, s_tmp);
-    __syncthreads();
-    PROF_MARK(12);
 }
 
 // ---------------------------------------------------------------------------
@@ -535,9 +675,13 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     const int64_t per = (total + grid - 1) / grid;
     // parts a row can be cut into: its share of the CTAs, plus one at either end
     const int64_t maxparts = parts_per_row > 0 ? parts_per_row : (nvv + per - 1) / per + 2;
-    if (maxparts * d.k > kMergeMaxSlots || maxparts > 1024)
+    // The CTA that merges a row gathers every part's list into one tile stage of its shared memory.
+    const int64_t merge_slots = kMergeMaxSlots;
+    static_assert(kMergeMaxSlots * 8 == kStreamThreads * kStreamVecs * 16, "a tile stage holds the gathered lists");
+    static_assert(kMergeMaxSlots == 2 * kStreamCandCap, "the candidate regions hold the selection scratch");
+    if (maxparts * d.k > merge_slots || maxparts > 1024)
         return VKOP_UNSUPPORTED;
-    int list_cap = static_cast<int>(kMergeMaxSlots / maxparts);
+    int list_cap = static_cast<int>(merge_slots / maxparts);
     if (list_cap > kStreamListCap)
         list_cap = kStreamListCap;
     plan->grid = static_cast<int>(grid);
@@ -548,10 +692,11 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     plan->parts_per_row = parts_per_row;
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
-    plan->counters_bytes = 0;
-    plan->lists_bytes = static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
+    // one arrival counter for the workspace; per row: an arrival counter for each of the two sets of
+    // lists, and the number of calls that have written the row's result
+    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 3 * 4 + 255) / 256) * 256;
+    plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
     plan->smem_bytes = 2 * static_cast<size_t>(kStreamThreads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamCandCap) * 8;
-    plan->select_smem_bytes = 2 * (static_cast<size_t>(maxparts) * list_cap + 32) * 8;
     return VKOP_OK;
 }
 
@@ -575,15 +720,11 @@ static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, cud
 
 template <typename T, bool ALIGNED>
 static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStream_t stream) {
-    int rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED>, static_cast<unsigned>(plan.grid),
-                        kStreamThreads, plan.smem_bytes, stream, p);
+    const int rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED>,
+                              static_cast<unsigned>(plan.grid), kStreamThreads, plan.smem_bytes, stream, p);
     if (rc != VKOP_OK)
         return rc;
-    rc = launch_pdl(softmax_topk_row_select_kernel<T, kSelectThreads>, static_cast<unsigned>(p.rows), kSelectThreads,
-                    plan.select_smem_bytes, stream, p, plan.grid);
-    if (rc != VKOP_OK)
-        return rc;
-    note_launch(2);
+    note_launch(1);
     return check_launch();
 }
 
@@ -608,8 +749,9 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.index_offset = d.index_offset;
     p.out_values = out_values;
     p.out_indices = out_indices;
-    p.counters = nullptr;
-    p.lists = reinterpret_cast<unsigned long long *>(workspace);
+    p.arrivals = reinterpret_cast<unsigned long long *>(workspace);
+    p.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(workspace) + 256);
+    p.lists = reinterpret_cast<unsigned long long *>(static_cast<char *>(workspace) + plan.counters_bytes);
     p.packets_out = reinterpret_cast<uint32_t *>(packets_out);
     p.nvv = plan.nvv;
     p.per_cta = plan.per_cta;
