@@ -18,7 +18,10 @@
  *   - nothing is allocated; scratch memory comes from the caller
  *     (`*_workspace` tells how much).  A workspace must be cleared once with
  *     vkop_cuda_workspace_init after it is allocated; kernels leave it ready
- *     for the next call.  One workspace serves one call in flight at a time;
+ *     for the next call with the same descriptor (clear it again before it
+ *     serves a different descriptor: the kernels keep counters in it whose
+ *     layout follows the shape).  Calls that share a workspace must be
+ *     enqueued on one stream, in order; they may then overlap on the device;
  *   - the return value is VKOP_OK (0) or a negative vkop_status; the library
  *     never throws and never aborts.
  */

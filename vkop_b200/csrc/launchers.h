@@ -29,7 +29,7 @@ int launch_merge(const vkop_softmax_topk_desc &d, const void *packets, int shard
 struct StreamPlan {
     int grid;
     int64_t per_cta, nvv, vstride;
-    int maxparts, list_cap, parts_per_row, aligned;
+    int maxparts, list_cap, parts_per_row, aligned, cluster, threads;
     size_t counters_bytes, lists_bytes, smem_bytes;
 };
 // base_aligned: the logits pointer is a multiple of 16 (rows then are too when the row stride is)

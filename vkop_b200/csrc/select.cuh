@@ -4,6 +4,8 @@
 // per-row merge of published candidate lists.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace vkop_cuda {
@@ -283,14 +285,17 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
 // streaming kernel keeps for its slot state; then the candidates.
 // s_buf holds the gathered candidates; s_sel is the scratch of the selection
 // (as many slots again), or null to take it right behind the candidates.
-template <typename T, int THREADS>
+// PEERS: the lists are not in global memory: list g sits at `lists` in the
+// shared memory of CTA g of this thread-block cluster (at most 32 lists of at
+// most 512 candidates).
+template <typename T, int THREADS, bool PEERS = false>
 __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned long long *lists, int64_t stride, int G,
                             uint64_t *s_buf, uint64_t *s_sel, float *s_red, int *s_int, int *s_tmp) {
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float M, S;
     int n;
-    if (G <= NW && p.list_cap <= 512) {
+    if (PEERS || (G <= NW && p.list_cap <= 512)) {
         // Few, short lists: warp g takes list g and fetches its header and its whole capacity in one
         // round trip (entries past the count are ignored).  One barrier later every warp knows all
         // headers: the largest of the parts' thresholds bounds the row's k-th best from below (that
@@ -299,14 +304,28 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
         unsigned long long regs[16];
         int cnt = 0;
         if (g < G) {
-            const unsigned long long *L = lists + g * stride;
-            const unsigned long long h0 = __ldcg(L), h1 = __ldcg(L + 1);
+            unsigned long long h0, h1;
+            if (PEERS) {
+                const unsigned long long *L = cooperative_groups::this_cluster().map_shared_rank(lists, g);
+                h0 = L[0];
+                h1 = L[1];
+                cnt = static_cast<int>(h1 & 0xFFFFu);
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const int i = lane + 32 * j;
-                regs[j] = i < p.list_cap ? __ldcg(L + 2 + i) : 0ull;
+                for (int j = 0; j < 16; j++) {
+                    const int i = lane + 32 * j;
+                    regs[j] = i < cnt ? L[2 + i] : 0ull;
+                }
+            } else {
+                const unsigned long long *L = lists + g * stride;
+                h0 = __ldcg(L);
+                h1 = __ldcg(L + 1);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int i = lane + 32 * j;
+                    regs[j] = i < p.list_cap ? __ldcg(L + 2 + i) : 0ull;
+                }
+                cnt = static_cast<int>(h1 & 0xFFFFu);
             }
-            cnt = static_cast<int>(h1 & 0xFFFFu);
             if (lane == 0) {
                 s_int[8 + g] = static_cast<int>(static_cast<uint32_t>(h1 >> 16));       // threshold key of the part
                 s_int[8 + NW + g] = static_cast<int>(static_cast<uint32_t>(h0));         // max z bits

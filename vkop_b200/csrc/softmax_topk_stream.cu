@@ -44,13 +44,15 @@
 
 namespace vkop_cuda {
 
-constexpr int kStreamThreads = 512;
+constexpr int kStreamThreads = 512;      // one call at a time: two CTAs per SM
+constexpr int kStreamThreadsSmall = 256; // calls that overlap: four lighter CTAs per SM hide each other's row ends
 constexpr int kStreamVecs = 4;
 constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
 constexpr int kUnit = 256;            // range boundaries inside a row are multiples of this many vectors
-constexpr int kStreamCandCap = 2048;  // candidate slots of one row part (= threads x private slots)
+constexpr int kStreamSlots = 4;       // private candidate slots of one thread
 constexpr int kStreamListCap = 512;   // most candidates one row part publishes
+constexpr int kStreamMaxCluster = 8;  // largest portable thread-block cluster
 
 // Snaps a slot offset inside a row to the nearest allowed boundary.
 __host__ __device__ inline uint32_t snap_in_row(uint32_t v, uint32_t nvv) {
@@ -95,12 +97,12 @@ __device__ inline uint32_t stream_owner(uint32_t V, uint32_t grid, uint32_t per,
     return c;
 }
 
-template <typename T, int THREADS, int VECS, bool ALIGNED>
+template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_kernel(const ChunkParams p) {
     constexpr int EPV = Elem<T>::kPerVec;
     constexpr int NW = THREADS / 32;
     constexpr int TV = THREADS * VECS;  // vectors per tile
-    constexpr int CAP = kStreamCandCap;
+    constexpr int CAP = kStreamSlots * THREADS;  // candidate slots of one row part
     extern __shared__ __align__(16) uint64_t s_dyn[];
     uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);  // two tile stages of TV vectors
     // First region: while a part streams, SLOTS private slots per thread (slot s of thread t at
@@ -117,33 +119,26 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     __shared__ int s_hist[256];
     __shared__ int s_pick[4];
     __shared__ int s_tmp[2];
-    __shared__ int s_int[8 + 1024];
+    __shared__ int s_int[8 + (THREADS >= 512 ? 1024 : 64)];  // merge: per-part header fields (parts <= 1024 / 64)
     __shared__ int s_count;
     __shared__ uint32_t s_epoch, s_tnew;
     __shared__ int s_flag[2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t grid = gridDim.x;
-    // The number of this call on its workspace: CTAs draw arrival tickets, and the next call is let
-    // in only after every CTA of this one has drawn (the barrier orders the draw before the signal),
-    // so the tickets of one call are one block of `grid` consecutive numbers.
-    if (tid == 0)
-        s_epoch = static_cast<uint32_t>(atomicAdd(p.arrivals, 1ull) / grid);
-    __syncthreads();
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // Calls alternate between two sets of scratch lists and arrival counters, so a call never has to
-    // wait for the row merges of the call right before it, only for those of the call before that.
-    const uint32_t epoch = s_epoch;
-    const int64_t set = epoch & 1u;
-    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
     const uint32_t nvv = static_cast<uint32_t>(p.nvv);
     const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
     const uint32_t per = static_cast<uint32_t>(p.per_cta);
     const uint32_t parts = static_cast<uint32_t>(p.parts_per_row);
     const uint32_t Vs = stream_boundary(blockIdx.x, grid, per, nvv, total, parts);
     const uint32_t Ve = stream_boundary(blockIdx.x + 1, grid, per, nvv, total, parts);
-    if (Ve <= Vs)
+    if (Ve <= Vs) {
+        if (CLUSTER) {  // (the planner gives every CTA of a cluster a part; keep the barriers matched anyway)
+            cooperative_groups::this_cluster().sync();
+            cooperative_groups::this_cluster().sync();
+        }
         return;
+    }
     int remaining = static_cast<int>(Ve - Vs);
     bool waited = false;
     if (!p.input_ready) {
@@ -201,6 +196,18 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     issue_tile(0, row, v0, nvt);
     PROF_MARK(0);
 
+    // ---- the place of this call among the calls that share its workspace (the first tile is on its
+    // way meanwhile).  Every CTA draws an arrival ticket; the next call is let in only after every
+    // CTA of this one has drawn (a barrier orders the draw before the signal), so the tickets of one
+    // call are `grid` consecutive numbers, which numbers the call.  Calls alternate between two sets
+    // of scratch lists and arrival counters, so a call never waits for the row merges of the call
+    // right before it, only for those of the call before that.
+    // CLUSTER (the CTAs of one row form a thread-block cluster and hand their parts over in shared
+    // memory) is used for calls that wait for their predecessor at once: nothing to number. ----
+    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
+    if (!CLUSTER && tid == 0)
+        s_epoch = static_cast<uint32_t>(atomicAdd(p.arrivals, 1ull) / grid);
+
     // ---- state of the current row part ----
     // Threshold groups: gs lanes form a group; the minimum over all groups (of full warps) of the group
     // maximum of the running thread maxima has at least one element per group at or above it, so gs is
@@ -241,6 +248,9 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     if (tid == 0)
         s_count = 0;
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t epoch = CLUSTER ? 0u : s_epoch;
+    const int64_t set = epoch & 1u;
 
     for (;;) {
         const int c_row = row;
@@ -451,12 +461,13 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
                                                : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
             const int pidx = static_cast<int>(blockIdx.x - c_first);
-            unsigned long long *rowlists = p.lists + (set * p.rows + c_row) * p.splits * lstride;
-            unsigned long long *mylist = rowlists + pidx * lstride;
+            unsigned long long *rowlists = CLUSTER ? nullptr : p.lists + (set * p.rows + c_row) * p.splits * lstride;
+            // where the part is published: scratch memory, or this CTA's second candidate region
+            unsigned long long *mylist = CLUSTER ? reinterpret_cast<unsigned long long *>(s_work) : rowlists + pidx * lstride;
             // This set of lists last served the call before the previous one: is that call's merge of
             // this row finished?  (Asked early, used after the reduction below.)
             unsigned int done_calls = 0;
-            if (tid == 0 && !waited)
+            if (!CLUSTER && tid == 0 && !waited)
                 asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(done_calls) : "l"(row_done + c_row) : "memory");
 
             // ---- statistics: per warp first, one barrier, then over the warps ----
@@ -497,7 +508,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 
             // Rare: the row's lists may still be in use.  Waiting for the whole previous call is always
             // enough (it has merged this row only after the call before it had).
-            if (!waited && !s_flag[0]) {
+            if (!CLUSTER && !waited && !s_flag[0]) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
             }
@@ -569,7 +580,9 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                     C = s_count;
                 }
                 if (C > p.list_cap) {
-                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
+                    // (scratch: the overflow list has been consumed; with a cluster the part is published
+                    // there, and the tile stages are free because no CTA of a cluster goes on to another row)
+                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, CLUSTER ? s_dyn : s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
                     C = kk;
                 } else {
                     for (int i = tid; i < C; i += THREADS)
@@ -580,50 +593,70 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             }
             PROF_MARK(5);
 
-            // ---- announce the part; the last part of a row to arrive merges the row ----
-            if (tid == 0) {
-                mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-                mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
-                const uint32_t c_end = parts > 0 ? c_first + parts - 1
-                                                 : stream_owner(static_cast<uint32_t>(c_row + 1) * nvv - 1, grid, per, nvv, total, parts);
-                const int nparts = static_cast<int>(c_end - c_first + 1);
-                // release: the list (written by all threads before the barrier) and the header; acquire:
-                // the lists of the parts that arrived earlier
-                unsigned int arrived;
-                unsigned int *ticket = p.counters + set * p.rows + c_row;
-                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
-                const bool last = arrived == static_cast<unsigned int>(nparts - 1);
-                int in_order = 1;
-                if (last) {
-                    *ticket = 0;  // ready for the next call that uses this set
-                    // results of one row are written in call order: has the previous call written its own?
-                    unsigned int d;
-                    asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(row_done + c_row) : "memory");
-                    in_order = d == epoch;
-                }
-                s_flag[1] = last ? nparts : 0;
-                s_flag[0] = in_order;
-            }
-            __syncthreads();
-            PROF_MARK(6);
-            const int nparts = s_flag[1];
-            if (nparts > 0) {
-                PROF_MARK(7);
-                if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
-                    asm volatile("griddepcontrol.wait;" ::: "memory");
-                    waited = true;
-                }
-                // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
-                // in flight), the two candidate regions serve the selection: kMergeMaxSlots slots each
-                uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
-                merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
-                __syncthreads();
-                // the row's result is written and its lists are read
+            if (CLUSTER) {
+                // ---- the parts of the row meet at the cluster barrier; the first CTA of the row merges
+                // them straight from the other CTAs' shared memory ----
                 if (tid == 0) {
-                    const unsigned int d = epoch + 1u;
-                    asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+                    mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
+                    mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
                 }
-                PROF_MARK(12);
+                cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+                cluster.sync();
+                PROF_MARK(6);
+                if (cluster.block_rank() == 0) {
+                    PROF_MARK(7);
+                    // (the tile stages are free: no CTA of a cluster goes on to another row)
+                    merge_lists<T, THREADS, true>(p, c_row, mylist, 0, static_cast<int>(parts), s_dyn, s_dyn + 2 * TV, s_red, s_int,
+                                                  s_tmp);
+                    PROF_MARK(12);
+                }
+                cluster.sync();  // the other CTAs keep their shared memory until it has been read
+            } else {
+            // ---- announce the part; the last part of a row to arrive merges the row ----
+                if (tid == 0) {
+                    mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
+                    mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
+                    const uint32_t c_end = parts > 0 ? c_first + parts - 1
+                                                     : stream_owner(static_cast<uint32_t>(c_row + 1) * nvv - 1, grid, per, nvv, total, parts);
+                    const int nparts = static_cast<int>(c_end - c_first + 1);
+                    // release: the list (written by all threads before the barrier) and the header; acquire:
+                    // the lists of the parts that arrived earlier
+                    unsigned int arrived;
+                    unsigned int *ticket = p.counters + set * p.rows + c_row;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
+                    const bool last = arrived == static_cast<unsigned int>(nparts - 1);
+                    int in_order = 1;
+                    if (last) {
+                        *ticket = 0;  // ready for the next call that uses this set
+                        // results of one row are written in call order: has the previous call written its own?
+                        unsigned int d;
+                        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(row_done + c_row) : "memory");
+                        in_order = d == epoch;
+                    }
+                    s_flag[1] = last ? nparts : 0;
+                    s_flag[0] = in_order;
+                }
+                __syncthreads();
+                PROF_MARK(6);
+                const int nparts = s_flag[1];
+                if (nparts > 0) {
+                    PROF_MARK(7);
+                    if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
+                        asm volatile("griddepcontrol.wait;" ::: "memory");
+                        waited = true;
+                    }
+                    // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
+                    // in flight), the two candidate regions serve the selection: 8 * THREADS slots each
+                    uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
+                    merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
+                    __syncthreads();
+                    // the row's result is written and its lists are read
+                    if (tid == 0) {
+                        const unsigned int d = epoch + 1u;
+                        asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+                    }
+                    PROF_MARK(12);
+                }
             }
             if (has_next) {
                 // ---- reset for the next row part ----
@@ -675,33 +708,46 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     const int64_t per = (total + grid - 1) / grid;
     // parts a row can be cut into: its share of the CTAs, plus one at either end
     const int64_t maxparts = parts_per_row > 0 ? parts_per_row : (nvv + per - 1) / per + 2;
-    // The CTA that merges a row gathers every part's list into one tile stage of its shared memory.
-    const int64_t merge_slots = kMergeMaxSlots;
-    static_assert(kMergeMaxSlots * 8 == kStreamThreads * kStreamVecs * 16, "a tile stage holds the gathered lists");
-    static_assert(kMergeMaxSlots == 2 * kStreamCandCap, "the candidate regions hold the selection scratch");
+    // Calls that may overlap their predecessor (the caller vouches for the logits) run as lighter
+    // CTAs, four to an SM: while some finish their row part, the others keep streaming.  A call that
+    // waits for its predecessor anyway runs as two large CTAs per SM, and with few parts per row the
+    // CTAs of a row form a cluster and hand their parts over in shared memory.
+    const bool overlapping = (d.flags & VKOP_FLAG_INPUT_READY) != 0;
+    int threads = kStreamThreads;
+    if (overlapping && parts_per_row > 0 && maxparts <= 64 && maxparts * d.k <= 8 * kStreamThreadsSmall)
+        threads = kStreamThreadsSmall;
+    // The CTA that merges a row gathers every part's list into one tile stage of its shared memory
+    // (8 * threads slots) and selects in the two candidate regions (as many again).
+    const int64_t merge_slots = 8 * static_cast<int64_t>(threads);
+    static_assert(kStreamVecs * 16 == 8 * 8 && 2 * kStreamSlots == 8, "a tile stage and the candidate regions hold 8 slots per thread");
     if (maxparts * d.k > merge_slots || maxparts > 1024)
         return VKOP_UNSUPPORTED;
     int list_cap = static_cast<int>(merge_slots / maxparts);
     if (list_cap > kStreamListCap)
         list_cap = kStreamListCap;
+    plan->threads = threads;
     plan->grid = static_cast<int>(grid);
     plan->per_cta = per;
     plan->nvv = nvv;
     plan->vstride = aligned ? stride * esz / 16 : 0;
     plan->aligned = aligned ? 1 : 0;
     plan->parts_per_row = parts_per_row;
+    // few parts per row: the CTAs of a row form a cluster and hand their parts over in shared memory
+    plan->cluster = (!overlapping && parts_per_row >= 1 && parts_per_row <= kStreamMaxCluster) ? parts_per_row : 0;
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
     // one arrival counter for the workspace; per row: an arrival counter for each of the two sets of
-    // lists, and the number of calls that have written the row's result
-    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 3 * 4 + 255) / 256) * 256;
+    // lists and the number of calls that have written the row's result (scratch lists), turns drawn
+    // and turns finished (clusters)
+    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 5 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
-    plan->smem_bytes = 2 * static_cast<size_t>(kStreamThreads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamCandCap) * 8;
+    plan->smem_bytes = 2 * static_cast<size_t>(threads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamSlots) * threads * 8;
     return VKOP_OK;
 }
 
+// cluster > 0: consecutive groups of `cluster` CTAs form thread-block clusters.
 template <typename Kern, typename... Args>
-static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream, Args... args) {
+static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, unsigned cluster, cudaStream_t stream, Args... args) {
     if (smem > 32 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return VKOP_CUDA_ERROR;
@@ -710,18 +756,34 @@ static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, cud
     cfg.blockDim = dim3(block);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (cluster > 0) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cluster;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? VKOP_OK : VKOP_CUDA_ERROR;
 }
 
 template <typename T, bool ALIGNED>
 static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStream_t stream) {
-    const int rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED>,
-                              static_cast<unsigned>(plan.grid), kStreamThreads, plan.smem_bytes, stream, p);
+    const unsigned grid = static_cast<unsigned>(plan.grid);
+    int rc;
+    if (plan.cluster > 0)
+        rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED, true>, grid, kStreamThreads,
+                        plan.smem_bytes, static_cast<unsigned>(plan.cluster), stream, p);
+    else if (plan.threads == kStreamThreadsSmall)
+        rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreadsSmall, kStreamVecs, ALIGNED, false>, grid,
+                        kStreamThreadsSmall, plan.smem_bytes, 0u, stream, p);
+    else
+        rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED, false>, grid, kStreamThreads,
+                        plan.smem_bytes, 0u, stream, p);
     if (rc != VKOP_OK)
         return rc;
     note_launch(1);

@@ -117,16 +117,32 @@ class Operator {
     }
 
     // Scratch memory owned by the operator (the role of Topk's temporary tensors, ops/Topk.hpp:46-54).
-    void *workspace(size_t bytes) {
+    // `shape_key` identifies the descriptor the scratch memory serves: the kernels keep counters in it
+    // whose layout follows the shape, so it is cleared again whenever the key changes.
+    void *workspace(size_t bytes, uint64_t shape_key = 0) {
         if (bytes == 0)
             return nullptr;
         if (!ws_ || ws_->bytes() < bytes) {
             ws_ = std::make_shared<core::DeviceBuffer>(bytes);
+            ws_key_ = shape_key + 1;  // force the clear below
+        }
+        if (ws_key_ != shape_key) {
             check(vkop_cuda_workspace_init(ws_->ptr(), ws_->bytes(), stream()), "workspace_init");
+            ws_key_ = shape_key;
         }
         return ws_->ptr();
     }
     size_t workspace_bytes() const { return ws_ ? ws_->bytes() : 0; }
+    // One number per distinct selection descriptor (shape, element type, k, path).
+    static uint64_t shape_key(const vkop_softmax_topk_desc &d) {
+        uint64_t h = 1469598103934665603ull;
+        const uint64_t parts[] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(d.cols), static_cast<uint64_t>(d.row_stride),
+                                  static_cast<uint64_t>(d.dtype), static_cast<uint64_t>(d.k), static_cast<uint64_t>(d.path),
+                                  static_cast<uint64_t>(d.splits), static_cast<uint64_t>(d.flags)};
+        for (uint64_t v : parts)
+            h = (h ^ v) * 1099511628211ull;
+        return h | 1ull;
+    }
 
     // Device storage of a tensor of one of the supported element types.
     void *device_of(const std::shared_ptr<core::ITensor> &t) {
@@ -191,6 +207,7 @@ class Operator {
 
   private:
     std::shared_ptr<core::DeviceBuffer> ws_;
+    uint64_t ws_key_ = 0;
 };
 
 inline std::atomic<int> Operator::instance_count_{0};

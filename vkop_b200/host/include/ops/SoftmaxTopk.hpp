@@ -50,7 +50,7 @@ class SoftmaxTopk : public Topk {
             throw std::invalid_argument("SoftmaxTopK: output tensors are too small");
         size_t need = 0;
         check(vkop_cuda_softmax_topk_workspace(&d, &need), "vkop_cuda_softmax_topk_workspace");
-        void *ws = workspace(need);
+        void *ws = workspace(need, shape_key(d));
         check(vkop_cuda_softmax_topk(&d, device_of(inputs[0]), device_of(outputs[0]), device_of(outputs[1]), ws, workspace_bytes(),
                                      stream()),
               "vkop_cuda_softmax_topk");
