@@ -205,6 +205,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
+    ap.add_argument("--graph-steps", type=int, default=64, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -267,12 +268,13 @@ def main():
         step(i, stream)
     barrier()
     graph = None
-    if not args.no_graph:
-        # the launch-bound loop is captured once (one launch per input buffer) and replayed
+    gsteps = max(NBUF, (args.graph_steps // NBUF) * NBUF)
+    if not args.no_graph and args.steps >= gsteps:
+        # the launch-bound loop is captured once (consecutive steps read different buffers) and replayed
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             cs = torch.cuda.current_stream().cuda_stream
-            for i in range(NBUF):
+            for i in range(gsteps):
                 step(i, cs)
         for _ in range(3):
             graph.replay()
@@ -283,9 +285,9 @@ def main():
     e0.record()
     done = 0
     if graph is not None:
-        for _ in range(args.steps // NBUF):
+        for _ in range(args.steps // gsteps):
             graph.replay()
-        done = (args.steps // NBUF) * NBUF
+        done = (args.steps // gsteps) * gsteps
     for i in range(done, args.steps):
         step(i, stream)
     e1.record()
@@ -364,7 +366,7 @@ def main():
             "config": {"workload": args.workload, "rows_per_gpu": rows, "cols": cols, "k": k, "inv_temperature": inv_t,
                        "sharding": f"rows x{world}" if world > 1 else "none",
                        "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * cols * bufs[0].element_size() >> 20} MiB) > L2",
-                       "path": args.path, "input_ready_flag": not args.serialize, "launch": "host" if graph is None else f"cuda graph of {NBUF} steps"},
+                       "path": args.path, "input_ready_flag": not args.serialize, "launch": "host" if graph is None else f"cuda graph of {gsteps} steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": abytes, "pct_of_8TBs": achieved / 8000.0 * 100.0},

@@ -461,9 +461,12 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
                                                : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
             const int pidx = static_cast<int>(blockIdx.x - c_first);
-            unsigned long long *rowlists = CLUSTER ? nullptr : p.lists + (set * p.rows + c_row) * p.splits * lstride;
+            // whole: this CTA holds the whole row (one part per row): nothing to publish, it selects itself
+            const bool whole = !CLUSTER && parts == 1;
+            const bool local = CLUSTER || whole;
+            unsigned long long *rowlists = local ? nullptr : p.lists + (set * p.rows + c_row) * p.splits * lstride;
             // where the part is published: scratch memory, or this CTA's second candidate region
-            unsigned long long *mylist = CLUSTER ? reinterpret_cast<unsigned long long *>(s_work) : rowlists + pidx * lstride;
+            unsigned long long *mylist = local ? reinterpret_cast<unsigned long long *>(s_work) : rowlists + pidx * lstride;
             // This set of lists last served the call before the previous one: is that call's merge of
             // this row finished?  (Asked early, used after the reduction below.)
             unsigned int done_calls = 0;
@@ -485,7 +488,8 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             }
             if (tid == 0) {
                 s_tmp[0] = 0;
-                s_flag[0] = static_cast<int>(done_calls - epoch + 1u) >= 0;  // calls 0 .. epoch - 2 are done
+                // scratch lists: calls 0 .. epoch - 2 are done with them; whole rows: results come in call order
+                s_flag[0] = whole ? done_calls == epoch : static_cast<int>(done_calls - epoch + 1u) >= 0;
             }
             __syncthreads();
             uint32_t mkey = lane < NW ? s_wm[0][lane] : 0u;
@@ -508,7 +512,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 
             // Rare: the row's lists may still be in use.  Waiting for the whole previous call is always
             // enough (it has merged this row only after the call before it had).
-            if (!CLUSTER && !waited && !s_flag[0]) {
+            if (!local && !waited && !s_flag[0]) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
             }
@@ -580,9 +584,9 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                     C = s_count;
                 }
                 if (C > p.list_cap) {
-                    // (scratch: the overflow list has been consumed; with a cluster the part is published
-                    // there, and the tile stages are free because no CTA of a cluster goes on to another row)
-                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, CLUSTER ? s_dyn : s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
+                    // (scratch: the overflow list has been consumed; a part that stays in shared memory is
+                    // published there, and the tile stages are free: such a CTA does not go on to another row)
+                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, local ? s_dyn : s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
                     C = kk;
                 } else {
                     for (int i = tid; i < C; i += THREADS)
@@ -611,6 +615,37 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                     PROF_MARK(12);
                 }
                 cluster.sync();  // the other CTAs keep their shared memory until it has been read
+            } else if (whole) {
+                // ---- the part is the row: select among its candidates and write the result.  Results of
+                // one row are written in call order; rarely the previous call has not written its own yet:
+                // then wait for all of it. ----
+                if (!waited && !s_flag[0]) {  // look once more before giving up
+                    if (tid == 0) {
+                        unsigned int dn;
+                        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done + c_row) : "memory");
+                        s_flag[1] = dn == epoch;
+                    }
+                    __syncthreads();
+                    if (!s_flag[1]) {
+                        asm volatile("griddepcontrol.wait;" ::: "memory");
+                        waited = true;
+                    }
+                }
+                PROF_MARK(7);
+                if (p.packets_out && tid == 0) {
+                    uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
+                    pk[0] = __float_as_uint(mz);
+                    pk[1] = __float_as_uint(S);
+                    pk[2] = static_cast<uint32_t>(C < p.k ? C : p.k);
+                    pk[3] = 0;
+                }
+                select_and_emit<T, THREADS>(p, c_row, reinterpret_cast<uint64_t *>(mylist + 2), C, s_dyn, mz, S, nullptr, s_tmp);
+                __syncthreads();
+                if (tid == 0) {
+                    const unsigned int d = epoch + 1u;
+                    asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+                }
+                PROF_MARK(12);
             } else {
             // ---- announce the part; the last part of a row to arrive merges the row ----
                 if (tid == 0) {
@@ -698,9 +733,19 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     const int64_t tiles = (total + tile - 1) / tile;
     int64_t grid = slots < tiles ? slots : tiles;
     int parts_per_row = 0;
+    // Calls that may overlap their predecessor (the caller vouches for the logits) fill the GPU
+    // together: a call takes about 64 CTAs, a whole row per CTA when there are that many rows, so
+    // that rows need no merge at all.  A call that waits for its predecessor spreads over all SMs.
+    const bool overlapping = (d.flags & VKOP_FLAG_INPUT_READY) != 0;
     if (d.rows <= slots / 2) {
-        const int64_t s = slots / d.rows;
-        if (nvv / s >= 2 * kUnit && d.rows * s <= tiles) {
+        int64_t s = slots / d.rows;
+        if (overlapping) {
+            const int64_t few = (64 + d.rows - 1) / d.rows;
+            s = few < s ? few : s;
+        }
+        if (d.splits > 0)
+            s = d.splits;  // the caller's choice of CTAs per row
+        if (s <= slots && nvv / s >= 2 * kUnit && d.rows * s <= tiles) {
             parts_per_row = static_cast<int>(s);  // the same number of CTAs for every row: no CTA crosses a row
             grid = d.rows * s;
         }
@@ -708,11 +753,10 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     const int64_t per = (total + grid - 1) / grid;
     // parts a row can be cut into: its share of the CTAs, plus one at either end
     const int64_t maxparts = parts_per_row > 0 ? parts_per_row : (nvv + per - 1) / per + 2;
-    // Calls that may overlap their predecessor (the caller vouches for the logits) run as lighter
-    // CTAs, four to an SM: while some finish their row part, the others keep streaming.  A call that
-    // waits for its predecessor anyway runs as two large CTAs per SM, and with few parts per row the
-    // CTAs of a row form a cluster and hand their parts over in shared memory.
-    const bool overlapping = (d.flags & VKOP_FLAG_INPUT_READY) != 0;
+    // Overlapping calls run as lighter CTAs, four to an SM: while some finish their row part, the
+    // others keep streaming.  A call that waits for its predecessor anyway runs as two large CTAs
+    // per SM, and with few parts per row the CTAs of a row form a cluster and hand their parts over
+    // in shared memory.
     int threads = kStreamThreads;
     if (overlapping && parts_per_row > 0 && maxparts <= 64 && maxparts * d.k <= 8 * kStreamThreadsSmall)
         threads = kStreamThreadsSmall;
