@@ -48,9 +48,10 @@ WORKLOADS = {
 }
 NBUF = 8
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the chunk kernel on llm_vocab_f32
-# (profiles/softmax_topk_chunk_llm_vocab_f32.md); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel, from the ncu
+# capture summarised in profiles/softmax_topk_stream_llm_vocab_f32_full.md; None for workloads
+# without a capture.
+NCU_TRAFFIC_BYTES = {"llm_vocab_f32": 33042176}
 
 
 def algorithmic_bytes(rows, cols, dtype, k):

@@ -279,15 +279,15 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
         // the current tile: this thread's own slots of the stage
         uint4 d[VECS];
-        {
-            const uint4 *src = s_tile + stage * TV;
+        uint4 *const cur = s_tile + stage * TV + tid;
 #pragma unroll
-            for (int j = 0; j < VECS; j++)
-                d[j] = src[j * THREADS + tid];
-        }
+        for (int j = 0; j < VECS; j++)
+            d[j] = cur[j * THREADS];
         stage ^= 1;
 
+        bool edited = false;  // the words differ from what the stage holds
         if (p.negate) {
+            edited = true;
             const uint32_t x = sizeof(T) == 4 ? 0x80000000u : 0x80008000u;
 #pragma unroll
             for (int j = 0; j < VECS; j++) {
@@ -298,6 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
         // ragged ends of the row: elements outside the row become -inf
         if ((!ALIGNED && c_v0 == 0) || (c_v0 + c_nvt >= nvr && (ALIGNED ? (cols % EPV != 0) : true))) {
+            edited = true;
 #pragma unroll
             for (int j = 0; j < VECS; j++) {
                 const int v = c_v0 + j * THREADS + tid;
@@ -308,6 +309,14 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                     mask_vector<T>(d[j], lo, hi);
                 }
             }
+        }
+
+        // The candidate filter further down reads the tile from the stage again (keeping the words in
+        // registers across the threshold refresh costs more than the few vectors it looks at).
+        if (edited) {
+#pragma unroll
+            for (int j = 0; j < VECS; j++)
+                cur[j * THREADS] = d[j];
         }
 
         // ---- maxima per vector and of the tile; online softmax statistics ----
@@ -432,7 +441,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             for (int j = 0; j < VECS; j++) {
                 if (!(vmax[j] < T_thr)) {
                     float f[EPV];
-                    Elem<T>::unpack(d[j], f);
+                    Elem<T>::unpack(cur[j * THREADS], f);
 #pragma unroll
                     for (int e = 0; e < EPV; e++) {
                         if (!(f[e] < T_thr))
@@ -444,7 +453,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 #pragma unroll
             for (int j = 0; j < VECS; j++) {
                 float f[EPV];
-                Elem<T>::unpack(d[j], f);
+                Elem<T>::unpack(cur[j * THREADS], f);
                 const int lv = j * THREADS + tid;
 #pragma unroll
                 for (int e = 0; e < EPV; e++) {
