@@ -172,6 +172,28 @@ int vkop_cuda_nms_workspace(const vkop_nms_desc *desc, size_t *bytes);
 int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scores, int32_t *out_rows,
                   int32_t *out_count, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ------------------------------------------------------------------------ */
+/* Fused Softmax + TopK that needs no workspace from the caller and allocates
+ * nothing: the chunk kernel works in a fixed array inside the loaded module
+ * (vkop_cuda_static_scratch_bytes() bytes of device memory per device).
+ *
+ * This entry point has no counterpart in the reference: there every operator
+ * allocates its temporaries itself (ops/Topk.hpp:134-152).  It is for callers
+ * that are given tensors and a stream and nothing else, or that must not call
+ * the allocator when they run (cudaMalloc synchronises the device and can
+ * fail under memory pressure).
+ *
+ * Same arguments and results as vkop_cuda_softmax_topk, without the
+ * workspace.  Limits: desc->path AUTO or CHUNK (the chunk kernel is used);
+ * VKOP_WORKSPACE_TOO_SMALL when the shape needs more scratch than the array
+ * holds.  The first call on a device looks up the array's device address and
+ * should come before any stream capture on that device.  All calls on a
+ * device share the array: calls that overlap on the GPU race on it, so order
+ * them (one stream, or events), or use the workspace entry point. */
+size_t vkop_cuda_static_scratch_bytes(void);
+int vkop_cuda_softmax_topk_static(const vkop_softmax_topk_desc *desc, const void *logits, void *out_values,
+                                  void *out_indices, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,6 +26,7 @@ EXPORTS = [
     "vkop_cuda_softmax_topk_workspace", "vkop_cuda_softmax_topk", "vkop_cuda_topk", "vkop_cuda_softmax",
     "vkop_cuda_packet_bytes", "vkop_cuda_softmax_topk_partial", "vkop_cuda_softmax_topk_merge",
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
+    "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
 ]
 
 
@@ -77,6 +78,8 @@ def lib() -> C.CDLL:
         L.vkop_cuda_softmax_topk_merge.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, C.c_int32, vp, vp, vp]
         L.vkop_cuda_nms_workspace.argtypes = [C.POINTER(NmsDesc), C.POINTER(sz)]
         L.vkop_cuda_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, vp, sz, vp]
+        L.vkop_cuda_static_scratch_bytes.restype = sz
+        L.vkop_cuda_softmax_topk_static.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp]
         _lib = L
     return _lib
 
@@ -158,6 +161,28 @@ def softmax_topk(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, ind
     fn = lib().vkop_cuda_topk if standalone_topk else lib().vkop_cuda_softmax_topk
     check(fn(C.byref(desc), logits.data_ptr(), values.data_ptr(), indices.data_ptr(), workspace.ptr,
              workspace.buf.numel(), _stream()), "topk" if standalone_topk else "softmax_topk")
+    return values, indices
+
+
+def static_scratch_bytes() -> int:
+    return int(lib().vkop_cuda_static_scratch_bytes())
+
+
+def softmax_topk_static(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, index_dtype: int = I32,
+                        value_kind: int = VALUE_PROBABILITY, out=None):
+    """Fused softmax + top-k through the entry point that takes no workspace and allocates nothing
+    (the outputs are still the caller's: pass `out`, or they are created here with torch)."""
+    if not logits.is_cuda:
+        raise RuntimeError("vkop_b200 runs on CUDA device memory only")
+    desc = make_desc(logits, k, inv_temperature, index_dtype, value_kind, True, PATH_AUTO, 0, 0, 0)
+    if out is None:
+        values = torch.empty((logits.shape[0], k), dtype=logits.dtype, device=logits.device)
+        indices = torch.empty((logits.shape[0], k), dtype=torch.int64 if index_dtype == I64 else torch.int32,
+                              device=logits.device)
+    else:
+        values, indices = out
+    check(lib().vkop_cuda_softmax_topk_static(C.byref(desc), logits.data_ptr(), values.data_ptr(), indices.data_ptr(),
+                                              _stream()), "softmax_topk_static")
     return values, indices
 
 

@@ -1,6 +1,7 @@
 // C ABI: argument validation and dispatch.  Declared in include/vkop_cuda.h.
 #include <atomic>
 #include <cmath>
+#include <mutex>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -232,6 +233,103 @@ int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scor
     if (need > 0 && (!workspace || workspace_bytes < need))
         return VKOP_WORKSPACE_TOO_SMALL;
     return launch_nms(*desc, boxes, scores, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Fused Softmax + TopK without a caller workspace.
+//
+// Some callers cannot hand over scratch memory.  An operator plugged into
+// somebody else's runtime is typically given its input and output tensors and
+// a stream and nothing else, and has no hook to ask the host application for
+// a buffer; and code on a latency-critical or memory-budgeted path must not
+// call the allocator when it runs, because cudaMalloc synchronises the whole
+// device and can fail once memory is fragmented or used up.  For them the
+// chunk kernel of this library can work in a fixed array that is part of the
+// loaded module: kStaticScratchBytes of device memory per device that uses
+// this entry point, present from module load to unload.
+//
+// What follows from that, for the caller:
+//   - nothing is allocated or freed, on the host or on the device, ever;
+//   - only descriptors whose scratch need fits the array are served
+//     (VKOP_WORKSPACE_TOO_SMALL otherwise; vkop_cuda_static_scratch_bytes()
+//     tells the size), and only on the chunk path (path AUTO or CHUNK);
+//   - the first call on a device looks the array's device address up
+//     (cudaGetSymbolAddress, with that device current) and should therefore
+//     come before any stream capture on that device;
+//   - all calls on a device share the one array and it keeps what the last
+//     call left there.  The kernels return their counters to zero; when the
+//     descriptor differs from the previous call's, the part of the array the
+//     new call uses is cleared first, on the call's stream.  Calls that
+//     overlap on the GPU (different streams without an ordering between them)
+//     race on the array: give them an order, or use the workspace entry point.
+namespace {
+constexpr size_t kStaticScratchBytes = 4u << 20;
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratchState {
+    void *ptr = nullptr;   // device address of g_static_scratch on this device (not the host-side symbol)
+    uint64_t key = 0;      // descriptor the array last served (0: none yet)
+};
+StaticScratchState g_static_state[kStaticMaxDevices];
+std::mutex g_static_mutex;
+
+uint64_t static_desc_key(const vkop_softmax_topk_desc &d) {
+    uint64_t h = 1469598103934665603ull;
+    const uint64_t parts[] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(d.cols), static_cast<uint64_t>(d.row_stride),
+                              static_cast<uint64_t>(d.dtype), static_cast<uint64_t>(d.k), static_cast<uint64_t>(d.splits)};
+    for (uint64_t v : parts)
+        h = (h ^ v) * 1099511628211ull;
+    return h | 1ull;
+}
+}  // namespace
+
+size_t vkop_cuda_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int vkop_cuda_softmax_topk_static(const vkop_softmax_topk_desc *desc, const void *logits, void *out_values,
+                                  void *out_indices, void *stream) {
+    if (!desc)
+        return VKOP_INVALID_ARG;
+    if (desc->path != VKOP_PATH_AUTO && desc->path != VKOP_PATH_CHUNK)
+        return VKOP_UNSUPPORTED;
+    vkop_softmax_topk_desc d = *desc;
+    d.path = VKOP_PATH_CHUNK;
+    size_t need = 0;
+    int rc = vkop_cuda_softmax_topk_workspace(&d, &need);
+    if (rc != VKOP_OK)
+        return rc;
+    if (need > kStaticScratchBytes)
+        return VKOP_WORKSPACE_TOO_SMALL;  // this shape needs more scratch than the built-in array holds
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess)
+        return VKOP_CUDA_ERROR;
+    if (dev < 0 || dev >= kStaticMaxDevices)
+        return VKOP_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratchState &st = g_static_state[dev];
+    if (!st.ptr) {
+        // once per device, with that device current: the symbol's address on THIS device
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return VKOP_CUDA_ERROR;
+        }
+        st.ptr = p;
+        st.key = 0;
+    }
+    const uint64_t key = static_desc_key(d);
+    if (st.key != key) {
+        // counters of this layout must start at zero; the array holds whatever the last call left
+        if (need > 0 && cudaMemsetAsync(st.ptr, 0, need, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+            cudaGetLastError();
+            return VKOP_CUDA_ERROR;
+        }
+        st.key = key;
+    }
+    rc = vkop_cuda_softmax_topk(&d, logits, out_values, out_indices, st.ptr, kStaticScratchBytes, stream);
+    if (rc != VKOP_OK)
+        st.key = 0;  // nothing is known about the array's contents after a failed call
+    return rc;
 }
 
 }  // extern "C"
