@@ -192,13 +192,65 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_nms(args, local_rank):
+    """Side line, not the headline metric: the NMS operator on the YOLO-style detect configuration
+    (16 images x 80 classes x 8400 anchors, threshold 0.25, per-class top-300, IoU 0.45, 300 kept)."""
+    from vkop_b200 import capi, workloads
+
+    torch.cuda.set_device(local_rank)
+    sets = []
+    for b in range(4):  # 4 x 45 MB of scores and boxes rotate: more than the L2 holds
+        boxes, scores = workloads.yolo_detect(seed=3 + b)
+        sets.append((boxes.cuda(), scores.cuda()))
+    B, Cn, N = sets[0][1].shape
+    cap = B * Cn * 300
+    rows = torch.empty((cap, 3), dtype=torch.int32, device="cuda")
+    count = torch.empty(1, dtype=torch.int32, device="cuda")
+    ws = None
+    steps = min(args.steps, 200)
+
+    def step(i):
+        nonlocal ws
+        bx, sc = sets[i % len(sets)]
+        if ws is None:
+            d = capi.NmsDesc(num_batch=B, num_class=Cn, num_boxes=N, capacity_rows=cap, **workloads.YOLO_PARAMS)
+            ws = capi.Workspace(capi.nms_workspace_bytes(d), bx.device)
+        capi.nms(bx, sc, capacity_rows=cap, workspace=ws, out=(rows, count), **workloads.YOLO_PARAMS)
+
+    n0 = capi.launch_count()
+    step(0)
+    per_step = capi.launch_count() - n0
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    peak, peak_kind = measured_peak()
+    nbytes = B * Cn * N * 4 + B * N * 16
+    print(json.dumps({
+        "metric": "nms_images_per_s", "value": B / (ms * 1e-3), "unit": "images/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "float32", "data": "synthetic",
+        "config": {"workload": "yolo_nms", "images": B, "classes": Cn, "anchors": N, "kept_rows": int(count.item()),
+                   "us_per_class_problem": ms * 1e3 / (B * Cn), "l2": "4 input sets (180 MB) rotate > L2"},
+        "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                     "note": "score scan only; the suppression sweep is latency-bound"},
+        "gpu_launches": per_step * steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llm_vocab_f32", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llm_vocab_f32", choices=sorted(WORKLOADS) + ["yolo_nms"])
     ap.add_argument("--splits", type=int, default=0, help="chunks per row (0 = automatic)")
     ap.add_argument("--path", default="auto", choices=["auto", "chunk", "stream", "radix"])
     ap.add_argument("--serialize", action="store_true",
@@ -220,6 +272,9 @@ def main():
         return
     args.steps = 2000 if args.steps is None else args.steps
     args.warmup = 20 if args.warmup is None else args.warmup
+    if args.workload == "yolo_nms":
+        run_nms(args, local_rank)
+        return
 
     from vkop_b200 import capi
 

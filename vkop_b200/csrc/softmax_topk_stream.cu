@@ -97,6 +97,304 @@ __device__ inline uint32_t stream_owner(uint32_t V, uint32_t grid, uint32_t per,
     return c;
 }
 
+// What the end of a row part needs from the streaming loop, by value.
+struct PartEnd {
+    float m_t, s_t;       // this thread's running maximum and exp-sum
+    uint32_t tkey;        // final threshold key of the part
+    uint64_t *slot;       // this thread's next private slot (tells how many it filled)
+    int c_row, c_v0, c_nvt, part_v0, head, nvr;
+    const uint4 *vbase;
+    int stage;            // tile stage that may hold a copy in flight
+    uint32_t epoch;       // number of this call on its workspace
+    bool has_next, waited;
+};
+// Shared-memory work areas of the streaming kernel (declared there).
+struct StreamShared {
+    uint32_t *wm0;
+    float *red;
+    int *hist, *pick, *tmp, *flag, *sint, *count;
+};
+
+// End of a row part: statistics, the part's candidate list, and whatever the launch shape asks for
+// next (cluster hand-over, direct selection of a whole row, or publication and the row merge by the
+// last part to arrive).  Returns whether the CTA has waited for the previous call by now.
+// Kept out of line on purpose: inlined, its many live values cost the streaming loop registers
+// (the loop spills and runs a third slower).
+template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER>
+__device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const PartEnd e, const StreamShared sh, uint64_t *s_dyn) {
+    constexpr int EPV = Elem<T>::kPerVec;
+    constexpr int NW = THREADS / 32;
+    constexpr int TV = THREADS * VECS;
+    constexpr int CAP = kStreamSlots * THREADS;
+    constexpr int SLOTS = kStreamSlots;
+    uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);
+    uint64_t *s_cand = s_dyn + 2 * TV * 2;
+    uint64_t *s_work = s_cand + CAP;
+    uint32_t *s_wm0 = sh.wm0;
+    float *s_red = sh.red;
+    int *s_hist = sh.hist, *s_pick = sh.pick, *s_tmp = sh.tmp, *s_flag = sh.flag, *s_int = sh.sint;
+    int &s_count = *sh.count;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t grid = gridDim.x;
+    const uint32_t nvv = static_cast<uint32_t>(p.nvv);
+    const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
+    const uint32_t per = static_cast<uint32_t>(p.per_cta);
+    const uint32_t parts = static_cast<uint32_t>(p.parts_per_row);
+    const float c1 = p.inv_t * kLog2e;
+    const int64_t lstride = 2 + p.list_cap;
+    const int cols = static_cast<int>(p.cols);
+    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
+    const float m_t = e.m_t, s_t = e.s_t;
+    const uint32_t tkey = e.tkey;
+    uint64_t *const slot = e.slot;
+    const int c_row = e.c_row, c_v0 = e.c_v0, c_nvt = e.c_nvt, part_v0 = e.part_v0, head = e.head, nvr = e.nvr;
+    const uint4 *const vbase = e.vbase;
+    const int stage = e.stage;
+    const uint32_t epoch = e.epoch;
+    const int64_t set = epoch & 1u;
+    const bool has_next = e.has_next;
+    (void)has_next;
+    bool waited = e.waited;
+    PROF_MARK(4);
+    // ================= end of a row part: statistics, publish, maybe merge the row =================
+    const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
+                                       : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
+    const int pidx = static_cast<int>(blockIdx.x - c_first);
+    // whole: this CTA holds the whole row (one part per row): nothing to publish, it selects itself
+    const bool whole = !CLUSTER && parts == 1;
+    const bool local = CLUSTER || whole;
+    unsigned long long *rowlists = local ? nullptr : p.lists + (set * p.rows + c_row) * p.splits * lstride;
+    // where the part is published: scratch memory, or this CTA's second candidate region
+    unsigned long long *mylist = local ? reinterpret_cast<unsigned long long *>(s_work) : rowlists + pidx * lstride;
+    // This set of lists last served the call before the previous one: is that call's merge of
+    // this row finished?  (Asked early, used after the reduction below.)
+    unsigned int done_calls = 0;
+    if (!CLUSTER && tid == 0 && !waited)
+        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(done_calls) : "l"(row_done + c_row) : "memory");
+
+    // ---- statistics: per warp first, one barrier, then over the warps ----
+    uint32_t wkey = order_key(m_t);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+        wkey = max(wkey, __shfl_xor_sync(kFullMask, wkey, o));
+    {
+        const float mw = key_to_float(wkey);
+        const float sw = warp_sum(m_t == -INFINITY ? 0.0f : s_t * ex2_approx((m_t - mw) * c1));
+        if (lane == 0) {
+            s_wm0[warp] = wkey;
+            s_red[warp] = sw;
+        }
+    }
+    if (tid == 0) {
+        s_tmp[0] = 0;
+        // scratch lists: calls 0 .. epoch - 2 are done with them; whole rows: results come in call order
+        s_flag[0] = whole ? done_calls == epoch : static_cast<int>(done_calls - epoch + 1u) >= 0;
+    }
+    __syncthreads();
+    uint32_t mkey = lane < NW ? s_wm0[lane] : 0u;
+    const float mw = key_to_float(mkey);
+    const float sw = lane < NW ? s_red[lane] : 0.0f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+        mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
+    const float mx = key_to_float(mkey);  // part maximum of the stored logits
+    const float S = warp_sum(sw != 0.0f ? sw * ex2_approx((mw - mx) * c1) : sw);  // (a NaN sum stays NaN)
+    const float mz = __fmul_rn(mx, p.inv_t);
+    const int novf = s_count;  // entries of the overflow list
+
+    const int part_v1 = c_v0 + c_nvt;
+    int e0 = part_v0 * EPV - head, e1 = part_v1 * EPV - head;
+    if (e0 < 0) e0 = 0;
+    if (e1 > cols) e1 = cols;
+    const int nvalid = e1 > e0 ? e1 - e0 : 0;
+    const int kk = nvalid < p.k ? nvalid : p.k;
+
+    // Rare: the row's lists may still be in use.  Waiting for the whole previous call is always
+    // enough (it has merged this row only after the call before it had).
+    if (!local && !waited && !s_flag[0]) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        waited = true;
+    }
+
+    // ---- candidates: private slots -> the part's list in scratch memory ----
+    // Entries kept under the weaker thresholds of the early tiles are dropped: at least k elements
+    // of this part reach the final threshold.  (No threshold: tkey is 0 and every entry stays.)
+    const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
+    uint32_t tpub = tkey;  // threshold the row merge may rely on
+    int C;
+    const bool plain = novf == 0 && !(p.need_sum && S != S);
+    if (plain) {
+#pragma unroll
+        for (int q = 0; q < SLOTS; q++) {
+            uint64_t ent = 0;
+            if (q < held)
+                ent = s_cand[q * THREADS + tid];
+            const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
+            const bool pass = q < held && key >= tkey;
+            const unsigned b = __ballot_sync(kFullMask, pass);
+            if (b != 0u) {
+                int base = 0;
+                if (lane == 0)
+                    base = atomicAdd(&s_tmp[0], __popc(b));
+                base = __shfl_sync(kFullMask, base, 0);
+                const int pos = base + __popc(b & ((1u << lane) - 1u));
+                if (pass && pos < p.list_cap)
+                    mylist[2 + pos] = make_cand(key, static_cast<uint32_t>(ent));
+            }
+        }
+        __syncthreads();
+        C = s_tmp[0];
+    } else {
+        C = p.list_cap + 1;
+    }
+    if (C > p.list_cap) {
+        // Rare: more candidates than a part may publish, threads that ran out of private slots,
+        // or NaN in the part (NaN ranks first but is invisible to the thread maxima).  Everything
+        // goes to one dense list in shared memory and the part's own k best are selected.
+        __syncthreads();
+        uint64_t mine[SLOTS];
+#pragma unroll
+        for (int q = 0; q < SLOTS; q++)
+            mine[q] = q < held ? s_cand[q * THREADS + tid] : 0ull;
+        if (tid == 0)
+            s_tmp[0] = 0;
+        __syncthreads();  // every private slot has been read: the region is free for the list
+        auto to_list = [&](uint64_t ent) {
+            const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
+            if (key >= tkey) {
+                const int pos = atomicAdd(&s_tmp[0], 1);
+                if (pos < CAP)
+                    s_cand[pos] = make_cand(key, static_cast<uint32_t>(ent));
+            }
+        };
+#pragma unroll
+        for (int q = 0; q < SLOTS; q++) {
+            if (q < held)
+                to_list(mine[q]);
+        }
+        for (int i = tid; i < (novf < CAP ? novf : CAP); i += THREADS)
+            to_list(s_work[i]);
+        __syncthreads();
+        C = s_tmp[0];
+        if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
+            // exact radix select over the part, re-read from L2
+            const int fv1 = part_v1 < nvr ? part_v1 : nvr;
+            select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, sh.count, s_hist, s_pick);
+            C = s_count;
+        }
+        if (C > p.list_cap) {
+            // (scratch: the overflow list has been consumed; a part that stays in shared memory is
+            // published there, and the tile stages are free: such a CTA does not go on to another row)
+            select_and_emit<T, THREADS>(p, c_row, s_cand, C, local ? s_dyn : s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
+            C = kk;
+        } else {
+            for (int i = tid; i < C; i += THREADS)
+                mylist[2 + i] = s_cand[i];
+        }
+        tpub = 0;  // the list holds the part's best, not everything above a threshold
+        __syncthreads();
+    }
+    PROF_MARK(5);
+
+    if (CLUSTER) {
+        // ---- the parts of the row meet at the cluster barrier; the first CTA of the row merges
+        // them straight from the other CTAs' shared memory ----
+        if (tid == 0) {
+            mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
+            mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
+        }
+        cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+        cluster.sync();
+        PROF_MARK(6);
+        if (cluster.block_rank() == 0) {
+            PROF_MARK(7);
+            // (the tile stages are free: no CTA of a cluster goes on to another row)
+            merge_lists<T, THREADS, true>(p, c_row, mylist, 0, static_cast<int>(parts), s_dyn, s_dyn + 2 * TV, s_red, s_int,
+                                          s_tmp);
+            PROF_MARK(12);
+        }
+        cluster.sync();  // the other CTAs keep their shared memory until it has been read
+    } else if (whole) {
+        // ---- the part is the row: select among its candidates and write the result.  Results of
+        // one row are written in call order; rarely the previous call has not written its own yet:
+        // then wait for all of it. ----
+        if (!waited && !s_flag[0]) {  // look once more before giving up
+            if (tid == 0) {
+                unsigned int dn;
+                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done + c_row) : "memory");
+                s_flag[1] = dn == epoch;
+            }
+            __syncthreads();
+            if (!s_flag[1]) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+            }
+        }
+        PROF_MARK(7);
+        if (p.packets_out && tid == 0) {
+            uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
+            pk[0] = __float_as_uint(mz);
+            pk[1] = __float_as_uint(S);
+            pk[2] = static_cast<uint32_t>(C < p.k ? C : p.k);
+            pk[3] = 0;
+        }
+        select_and_emit<T, THREADS>(p, c_row, reinterpret_cast<uint64_t *>(mylist + 2), C, s_dyn, mz, S, nullptr, s_tmp);
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int d = epoch + 1u;
+            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+        }
+        PROF_MARK(12);
+    } else {
+    // ---- announce the part; the last part of a row to arrive merges the row ----
+        if (tid == 0) {
+            mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
+            mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
+            const uint32_t c_end = parts > 0 ? c_first + parts - 1
+                                             : stream_owner(static_cast<uint32_t>(c_row + 1) * nvv - 1, grid, per, nvv, total, parts);
+            const int nparts = static_cast<int>(c_end - c_first + 1);
+            // release: the list (written by all threads before the barrier) and the header; acquire:
+            // the lists of the parts that arrived earlier
+            unsigned int arrived;
+            unsigned int *ticket = p.counters + set * p.rows + c_row;
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
+            const bool last = arrived == static_cast<unsigned int>(nparts - 1);
+            int in_order = 1;
+            if (last) {
+                *ticket = 0;  // ready for the next call that uses this set
+                // results of one row are written in call order: has the previous call written its own?
+                unsigned int d;
+                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(row_done + c_row) : "memory");
+                in_order = d == epoch;
+            }
+            s_flag[1] = last ? nparts : 0;
+            s_flag[0] = in_order;
+        }
+        __syncthreads();
+        PROF_MARK(6);
+        const int nparts = s_flag[1];
+        if (nparts > 0) {
+            PROF_MARK(7);
+            if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+            }
+            // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
+            // in flight), the two candidate regions serve the selection: 8 * THREADS slots each
+            uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
+            merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
+            __syncthreads();
+            // the row's result is written and its lists are read
+            if (tid == 0) {
+                const unsigned int d = epoch + 1u;
+                asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
+            }
+            PROF_MARK(12);
+        }
+    }
+    return waited;
+}
+
 template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_kernel(const ChunkParams p) {
     constexpr int EPV = Elem<T>::kPerVec;
@@ -147,7 +445,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     }
     const uint32_t filler = Elem<T>::kNegInfWord;
     const float c1 = p.inv_t * kLog2e;
-    const int64_t lstride = 2 + p.list_cap;
     const int cols = static_cast<int>(p.cols);
 
     // Geometry of a row: element offset of the row start inside its first vector, vectors that hold
@@ -173,7 +470,21 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         nvt = remaining;
     bool part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
 
+    // this thread's first slot of stage 0, as a shared-memory address
+    const uint32_t sdst0 = static_cast<uint32_t>(__cvta_generic_to_shared(s_tile + tid));
     auto issue_tile = [&](int stage, int r, int tv0, int tn) {
+        if (ALIGNED && tn == TV) {
+            // a full tile of an aligned row: four copies at fixed offsets, nothing to test
+            const char *g = reinterpret_cast<const char *>(reinterpret_cast<const uint4 *>(p.logits) +
+                                                           static_cast<int64_t>(r) * p.vstride + tv0 + tid);
+            const uint32_t sdst = sdst0 + static_cast<uint32_t>(stage) * (TV * 16);
+#pragma unroll
+            for (int j = 0; j < VECS; j++)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sdst + j * THREADS * 16), "l"(g + j * THREADS * 16)
+                             : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
         int head, nvr;
         const uint4 *vbase;
         row_geom(r, head, nvr, vbase);
@@ -204,7 +515,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     // right before it, only for those of the call before that.
     // CLUSTER (the CTAs of one row form a thread-block cluster and hand their parts over in shared
     // memory) is used for calls that wait for their predecessor at once: nothing to number. ----
-    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
     if (!CLUSTER && tid == 0)
         s_epoch = static_cast<uint32_t>(atomicAdd(p.arrivals, 1ull) / grid);
 
@@ -250,7 +560,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t epoch = CLUSTER ? 0u : s_epoch;
-    const int64_t set = epoch & 1u;
 
     for (;;) {
         const int c_row = row;
@@ -465,243 +774,32 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
 
         if (c_last) {
-            PROF_MARK(4);
-            // ================= end of a row part: statistics, publish, maybe merge the row =================
-            const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
-                                               : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
-            const int pidx = static_cast<int>(blockIdx.x - c_first);
-            // whole: this CTA holds the whole row (one part per row): nothing to publish, it selects itself
-            const bool whole = !CLUSTER && parts == 1;
-            const bool local = CLUSTER || whole;
-            unsigned long long *rowlists = local ? nullptr : p.lists + (set * p.rows + c_row) * p.splits * lstride;
-            // where the part is published: scratch memory, or this CTA's second candidate region
-            unsigned long long *mylist = local ? reinterpret_cast<unsigned long long *>(s_work) : rowlists + pidx * lstride;
-            // This set of lists last served the call before the previous one: is that call's merge of
-            // this row finished?  (Asked early, used after the reduction below.)
-            unsigned int done_calls = 0;
-            if (!CLUSTER && tid == 0 && !waited)
-                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(done_calls) : "l"(row_done + c_row) : "memory");
-
-            // ---- statistics: per warp first, one barrier, then over the warps ----
-            uint32_t wkey = order_key(m_t);
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1)
-                wkey = max(wkey, __shfl_xor_sync(kFullMask, wkey, o));
-            {
-                const float mw = key_to_float(wkey);
-                const float sw = warp_sum(m_t == -INFINITY ? 0.0f : s_t * ex2_approx((m_t - mw) * c1));
-                if (lane == 0) {
-                    s_wm[0][warp] = wkey;
-                    s_red[warp] = sw;
-                }
-            }
-            if (tid == 0) {
-                s_tmp[0] = 0;
-                // scratch lists: calls 0 .. epoch - 2 are done with them; whole rows: results come in call order
-                s_flag[0] = whole ? done_calls == epoch : static_cast<int>(done_calls - epoch + 1u) >= 0;
-            }
-            __syncthreads();
-            uint32_t mkey = lane < NW ? s_wm[0][lane] : 0u;
-            const float mw = key_to_float(mkey);
-            const float sw = lane < NW ? s_red[lane] : 0.0f;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1)
-                mkey = max(mkey, __shfl_xor_sync(kFullMask, mkey, o));
-            const float mx = key_to_float(mkey);  // part maximum of the stored logits
-            const float S = warp_sum(sw != 0.0f ? sw * ex2_approx((mw - mx) * c1) : sw);  // (a NaN sum stays NaN)
-            const float mz = __fmul_rn(mx, p.inv_t);
-            const int novf = s_count;  // entries of the overflow list
-
-            const int part_v1 = c_v0 + c_nvt;
-            int e0 = part_v0 * EPV - head, e1 = part_v1 * EPV - head;
-            if (e0 < 0) e0 = 0;
-            if (e1 > cols) e1 = cols;
-            const int nvalid = e1 > e0 ? e1 - e0 : 0;
-            const int kk = nvalid < p.k ? nvalid : p.k;
-
-            // Rare: the row's lists may still be in use.  Waiting for the whole previous call is always
-            // enough (it has merged this row only after the call before it had).
-            if (!local && !waited && !s_flag[0]) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                waited = true;
-            }
-
-            // ---- candidates: private slots -> the part's list in scratch memory ----
-            // Entries kept under the weaker thresholds of the early tiles are dropped: at least k elements
-            // of this part reach the final threshold.  (No threshold: tkey is 0 and every entry stays.)
-            const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
-            uint32_t tpub = tkey;  // threshold the row merge may rely on
-            int C;
-            const bool plain = novf == 0 && !(p.need_sum && S != S);
-            if (plain) {
-#pragma unroll
-                for (int q = 0; q < SLOTS; q++) {
-                    uint64_t ent = 0;
-                    if (q < held)
-                        ent = s_cand[q * THREADS + tid];
-                    const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
-                    const bool pass = q < held && key >= tkey;
-                    const unsigned b = __ballot_sync(kFullMask, pass);
-                    if (b != 0u) {
-                        int base = 0;
-                        if (lane == 0)
-                            base = atomicAdd(&s_tmp[0], __popc(b));
-                        base = __shfl_sync(kFullMask, base, 0);
-                        const int pos = base + __popc(b & ((1u << lane) - 1u));
-                        if (pass && pos < p.list_cap)
-                            mylist[2 + pos] = make_cand(key, static_cast<uint32_t>(ent));
-                    }
-                }
-                __syncthreads();
-                C = s_tmp[0];
-            } else {
-                C = p.list_cap + 1;
-            }
-            if (C > p.list_cap) {
-                // Rare: more candidates than a part may publish, threads that ran out of private slots,
-                // or NaN in the part (NaN ranks first but is invisible to the thread maxima).  Everything
-                // goes to one dense list in shared memory and the part's own k best are selected.
-                __syncthreads();
-                uint64_t mine[SLOTS];
-#pragma unroll
-                for (int q = 0; q < SLOTS; q++)
-                    mine[q] = q < held ? s_cand[q * THREADS + tid] : 0ull;
-                if (tid == 0)
-                    s_tmp[0] = 0;
-                __syncthreads();  // every private slot has been read: the region is free for the list
-                auto to_list = [&](uint64_t ent) {
-                    const uint32_t key = order_key(__uint_as_float(static_cast<uint32_t>(ent >> 32)));
-                    if (key >= tkey) {
-                        const int pos = atomicAdd(&s_tmp[0], 1);
-                        if (pos < CAP)
-                            s_cand[pos] = make_cand(key, static_cast<uint32_t>(ent));
-                    }
-                };
-#pragma unroll
-                for (int q = 0; q < SLOTS; q++) {
-                    if (q < held)
-                        to_list(mine[q]);
-                }
-                for (int i = tid; i < (novf < CAP ? novf : CAP); i += THREADS)
-                    to_list(s_work[i]);
-                __syncthreads();
-                C = s_tmp[0];
-                if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
-                    // exact radix select over the part, re-read from L2
-                    const int fv1 = part_v1 < nvr ? part_v1 : nvr;
-                    select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, &s_count, s_hist, s_pick);
-                    C = s_count;
-                }
-                if (C > p.list_cap) {
-                    // (scratch: the overflow list has been consumed; a part that stays in shared memory is
-                    // published there, and the tile stages are free: such a CTA does not go on to another row)
-                    select_and_emit<T, THREADS>(p, c_row, s_cand, C, local ? s_dyn : s_work, 0.0f, 0.0f, mylist + 2, s_tmp);
-                    C = kk;
-                } else {
-                    for (int i = tid; i < C; i += THREADS)
-                        mylist[2 + i] = s_cand[i];
-                }
-                tpub = 0;  // the list holds the part's best, not everything above a threshold
-                __syncthreads();
-            }
-            PROF_MARK(5);
-
-            if (CLUSTER) {
-                // ---- the parts of the row meet at the cluster barrier; the first CTA of the row merges
-                // them straight from the other CTAs' shared memory ----
-                if (tid == 0) {
-                    mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-                    mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
-                }
-                cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
-                cluster.sync();
-                PROF_MARK(6);
-                if (cluster.block_rank() == 0) {
-                    PROF_MARK(7);
-                    // (the tile stages are free: no CTA of a cluster goes on to another row)
-                    merge_lists<T, THREADS, true>(p, c_row, mylist, 0, static_cast<int>(parts), s_dyn, s_dyn + 2 * TV, s_red, s_int,
-                                                  s_tmp);
-                    PROF_MARK(12);
-                }
-                cluster.sync();  // the other CTAs keep their shared memory until it has been read
-            } else if (whole) {
-                // ---- the part is the row: select among its candidates and write the result.  Results of
-                // one row are written in call order; rarely the previous call has not written its own yet:
-                // then wait for all of it. ----
-                if (!waited && !s_flag[0]) {  // look once more before giving up
-                    if (tid == 0) {
-                        unsigned int dn;
-                        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done + c_row) : "memory");
-                        s_flag[1] = dn == epoch;
-                    }
-                    __syncthreads();
-                    if (!s_flag[1]) {
-                        asm volatile("griddepcontrol.wait;" ::: "memory");
-                        waited = true;
-                    }
-                }
-                PROF_MARK(7);
-                if (p.packets_out && tid == 0) {
-                    uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
-                    pk[0] = __float_as_uint(mz);
-                    pk[1] = __float_as_uint(S);
-                    pk[2] = static_cast<uint32_t>(C < p.k ? C : p.k);
-                    pk[3] = 0;
-                }
-                select_and_emit<T, THREADS>(p, c_row, reinterpret_cast<uint64_t *>(mylist + 2), C, s_dyn, mz, S, nullptr, s_tmp);
-                __syncthreads();
-                if (tid == 0) {
-                    const unsigned int d = epoch + 1u;
-                    asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
-                }
-                PROF_MARK(12);
-            } else {
-            // ---- announce the part; the last part of a row to arrive merges the row ----
-                if (tid == 0) {
-                    mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-                    mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
-                    const uint32_t c_end = parts > 0 ? c_first + parts - 1
-                                                     : stream_owner(static_cast<uint32_t>(c_row + 1) * nvv - 1, grid, per, nvv, total, parts);
-                    const int nparts = static_cast<int>(c_end - c_first + 1);
-                    // release: the list (written by all threads before the barrier) and the header; acquire:
-                    // the lists of the parts that arrived earlier
-                    unsigned int arrived;
-                    unsigned int *ticket = p.counters + set * p.rows + c_row;
-                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
-                    const bool last = arrived == static_cast<unsigned int>(nparts - 1);
-                    int in_order = 1;
-                    if (last) {
-                        *ticket = 0;  // ready for the next call that uses this set
-                        // results of one row are written in call order: has the previous call written its own?
-                        unsigned int d;
-                        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(row_done + c_row) : "memory");
-                        in_order = d == epoch;
-                    }
-                    s_flag[1] = last ? nparts : 0;
-                    s_flag[0] = in_order;
-                }
-                __syncthreads();
-                PROF_MARK(6);
-                const int nparts = s_flag[1];
-                if (nparts > 0) {
-                    PROF_MARK(7);
-                    if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
-                        asm volatile("griddepcontrol.wait;" ::: "memory");
-                        waited = true;
-                    }
-                    // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
-                    // in flight), the two candidate regions serve the selection: 8 * THREADS slots each
-                    uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
-                    merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
-                    __syncthreads();
-                    // the row's result is written and its lists are read
-                    if (tid == 0) {
-                        const unsigned int d = epoch + 1u;
-                        asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
-                    }
-                    PROF_MARK(12);
-                }
-            }
+            PartEnd e;
+            e.m_t = m_t;
+            e.s_t = s_t;
+            e.tkey = tkey;
+            e.slot = slot;
+            e.c_row = c_row;
+            e.c_v0 = c_v0;
+            e.c_nvt = c_nvt;
+            e.part_v0 = part_v0;
+            e.head = head;
+            e.nvr = nvr;
+            e.vbase = vbase;
+            e.stage = stage;
+            e.epoch = epoch;
+            e.has_next = has_next;
+            e.waited = waited;
+            StreamShared sh;
+            sh.wm0 = s_wm[0];
+            sh.red = s_red;
+            sh.hist = s_hist;
+            sh.pick = s_pick;
+            sh.tmp = s_tmp;
+            sh.flag = s_flag;
+            sh.sint = s_int;
+            sh.count = &s_count;
+            waited = stream_finish_part<T, THREADS, VECS, ALIGNED, CLUSTER>(p, e, sh, s_dyn);
             if (has_next) {
                 // ---- reset for the next row part ----
                 __syncthreads();  // every thread is done with the candidate regions and the counters
@@ -746,8 +844,8 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     // together: a call takes about 64 CTAs, a whole row per CTA when there are that many rows, so
     // that rows need no merge at all.  A call that waits for its predecessor spreads over all SMs.
     const bool overlapping = (d.flags & VKOP_FLAG_INPUT_READY) != 0;
-    if (d.rows <= slots / 2) {
-        int64_t s = slots / d.rows;
+    if (d.rows <= slots / 2 || overlapping) {
+        int64_t s = slots / d.rows > 0 ? slots / d.rows : 1;
         if (overlapping) {
             const int64_t few = (64 + d.rows - 1) / d.rows;
             s = few < s ? few : s;
