@@ -97,6 +97,91 @@ __device__ inline uint32_t stream_owner(uint32_t V, uint32_t grid, uint32_t per,
     return c;
 }
 
+// A lower bound of the k-th largest element of the part seen so far, from the running thread
+// maxima (m_t of every thread of the CTA; 0 = no bound).  Any value that at least k thread maxima
+// reach is valid, since they are k different elements.  First a coarse pair: lo, the smallest
+// maximum over at least k groups of gs lanes (valid, but several times too many elements reach it),
+// and hi, the smallest maximum over a few large groups (usually above the k-th largest).  Then a
+// histogram of the thread maxima between lo and hi, 256 bins, picks the highest bin edge that k
+// maxima still reach.  Two CTA barriers.  sh_hnext is cleared for the refresh after this one.
+// Out of line: it runs on a few tiles only and must not cost the streaming loop registers.
+template <int THREADS>
+__device__ __noinline__ uint32_t stream_refresh_threshold(float m_t, int k, int gs, int nfullw, int hgroups, uint32_t *sh_wr,
+                                                          uint32_t *sh_wm, int *sh_hist, int *sh_hnext, uint32_t *sh_tnew) {
+    constexpr int NW = THREADS / 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t key = order_key(m_t);
+    uint32_t glo = key;
+    if (gs > 0 && warp < nfullw) {
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t other = __shfl_xor_sync(kFullMask, glo, o);
+            glo = o < gs ? max(glo, other) : min(glo, other);  // maximum inside a group, minimum over groups
+        }
+    } else {
+        glo = gs > 0 ? 0xFFFFFFFFu : 0u;  // a partly filled warp does not constrain the threshold
+    }
+    const uint32_t wmax = __reduce_max_sync(kFullMask, key);
+    if (lane == 0) {
+        sh_wr[warp] = glo;
+        sh_wm[warp] = wmax;
+    }
+    __syncthreads();
+    if (tid < 256)
+        sh_hnext[tid] = 0;  // the histogram of the refresh after this one (everybody is done with it)
+    uint32_t lo = lane < NW ? sh_wr[lane] : 0xFFFFFFFFu;
+    lo = __reduce_min_sync(kFullMask, lo);
+    // hi: warps are paired up into hgroups groups; the smallest group maximum
+    uint32_t hi = 0xFFFFFFFFu;
+    if (lane < hgroups) {
+        hi = 0u;
+        for (int w = lane; w < NW; w += hgroups)
+            hi = max(hi, sh_wm[w]);
+    }
+    hi = __reduce_min_sync(kFullMask, hi);
+    uint32_t t_new = lo;
+    if (lo != 0u && hi > lo) {  // (the same for every thread of the CTA)
+        const uint32_t range = hi - lo;
+        const int shift = range > 255u ? 24 - __clz(range) : 0;  // range >> shift <= 255
+        if (key >= lo) {
+            const uint32_t b = (key - lo) >> shift;
+            atomicAdd(&sh_hist[b < 255u ? b : 255u], 1);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns bins 8l .. 8l+7; suffix counts over the lanes, then inside the lane that crosses k
+            const int4 h0 = *reinterpret_cast<const int4 *>(&sh_hist[8 * lane]);
+            const int4 h1 = *reinterpret_cast<const int4 *>(&sh_hist[8 * lane + 4]);
+            const int own = h0.x + h0.y + h0.z + h0.w + h1.x + h1.y + h1.z + h1.w;
+            int suf = own;  // maxima in the bins of this lane and of the lanes above
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_down_sync(kFullMask, suf, o);
+                if (lane + o < 32)
+                    suf += v;
+            }
+            const unsigned reach = __ballot_sync(kFullMask, suf >= k);  // lane 0 always does: lo is valid
+            if (lane == 31 - __clz(reach)) {
+                const int c[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+                int acc = suf - own, bin = 8 * lane;
+                bool found = false;
+#pragma unroll
+                for (int q = 7; q >= 0; q--) {
+                    acc += c[q];
+                    if (!found && acc >= k) {
+                        found = true;
+                        bin = 8 * lane + q;
+                    }
+                }
+                (*sh_tnew) = lo + (static_cast<uint32_t>(bin) << shift);
+            }
+        }
+        __syncthreads();
+        t_new = (*sh_tnew);
+    }
+    return t_new;
+}
+
 // What the end of a row part needs from the streaming loop, by value.
 struct PartEnd {
     float m_t, s_t;       // this thread's running maximum and exp-sum
@@ -422,7 +507,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     __shared__ uint32_t s_epoch, s_tnew;
     __shared__ int s_flag[2];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const uint32_t grid = gridDim.x;
     const uint32_t nvv = static_cast<uint32_t>(p.nvv);
     const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
@@ -660,81 +745,10 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
 
         // ---- threshold refresh from the running thread maxima: on tiles 0, 1, 3, 7, ... of the part and
         // on its last tile (the threshold settles quickly); the other tiles need no barrier at all.
-        // Any T that at least k thread maxima reach is a valid bound, since they are k different
-        // elements of the part.  First a coarse pair: lo, the smallest maximum over at least k groups of
-        // lanes (valid, but several times too many elements reach it), and hi, the smallest maximum
-        // over a few large groups (usually above the k-th largest).  Then a histogram of the thread
-        // maxima between lo and hi, 256 bins, picks the highest bin edge that k maxima still reach. ----
+        // (stream_refresh_threshold) ----
         if ((part_tile & (part_tile + 1)) == 0 || c_last) {
-            const uint32_t key = order_key(m_t);
-            uint32_t glo = key;
-            if (gs > 0 && warp < nfullw) {
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t other = __shfl_xor_sync(kFullMask, glo, o);
-                    glo = o < gs ? max(glo, other) : min(glo, other);  // maximum inside a group, minimum over groups
-                }
-            } else {
-                glo = gs > 0 ? 0xFFFFFFFFu : 0u;  // a partly filled warp does not constrain the threshold
-            }
-            const uint32_t wmax = __reduce_max_sync(kFullMask, key);
-            if (lane == 0) {
-                s_wr[parity][warp] = glo;
-                s_wm[parity][warp] = wmax;
-            }
-            __syncthreads();
-            if (tid < 256)
-                s_thist[parity ^ 1][tid] = 0;  // the histogram of the refresh after this one (everybody is done with it)
-            uint32_t lo = lane < NW ? s_wr[parity][lane] : 0xFFFFFFFFu;
-            lo = __reduce_min_sync(kFullMask, lo);
-            // hi: warps are paired up into hgroups groups; the smallest group maximum
-            uint32_t hi = 0xFFFFFFFFu;
-            if (lane < hgroups) {
-                hi = 0u;
-                for (int w = lane; w < NW; w += hgroups)
-                    hi = max(hi, s_wm[parity][w]);
-            }
-            hi = __reduce_min_sync(kFullMask, hi);
-            uint32_t t_new = lo;
-            if (lo != 0u && hi > lo) {  // (the same for every thread of the CTA)
-                const uint32_t range = hi - lo;
-                const int shift = range > 255u ? 24 - __clz(range) : 0;  // range >> shift <= 255
-                if (key >= lo) {
-                    const uint32_t b = (key - lo) >> shift;
-                    atomicAdd(&s_thist[parity][b < 255u ? b : 255u], 1);
-                }
-                __syncthreads();
-                if (warp == 0) {
-                    // lane l owns bins 8l .. 8l+7; suffix counts over the lanes, then inside the lane that crosses k
-                    const int4 h0 = *reinterpret_cast<const int4 *>(&s_thist[parity][8 * lane]);
-                    const int4 h1 = *reinterpret_cast<const int4 *>(&s_thist[parity][8 * lane + 4]);
-                    const int own = h0.x + h0.y + h0.z + h0.w + h1.x + h1.y + h1.z + h1.w;
-                    int suf = own;  // maxima in the bins of this lane and of the lanes above
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const int v = __shfl_down_sync(kFullMask, suf, o);
-                        if (lane + o < 32)
-                            suf += v;
-                    }
-                    const unsigned reach = __ballot_sync(kFullMask, suf >= p.k);  // lane 0 always does: lo is valid
-                    if (lane == 31 - __clz(reach)) {
-                        const int c[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-                        int acc = suf - own, bin = 8 * lane;
-                        bool found = false;
-#pragma unroll
-                        for (int q = 7; q >= 0; q--) {
-                            acc += c[q];
-                            if (!found && acc >= p.k) {
-                                found = true;
-                                bin = 8 * lane + q;
-                            }
-                        }
-                        s_tnew = lo + (static_cast<uint32_t>(bin) << shift);
-                    }
-                }
-                __syncthreads();
-                t_new = s_tnew;
-            }
+            const uint32_t t_new = stream_refresh_threshold<THREADS>(m_t, p.k, gs, nfullw, hgroups, s_wr[parity], s_wm[parity],
+                                                                     s_thist[parity], s_thist[parity ^ 1], &s_tnew);
             tkey = t_new > tkey ? t_new : tkey;
             T_thr = key_to_float(tkey);
             parity ^= 1;
