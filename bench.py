@@ -51,7 +51,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel, from the ncu
 # capture summarised in profiles/softmax_topk_stream_llm_vocab_f32_full.md; None for workloads
 # without a capture.
-NCU_TRAFFIC_BYTES = {"llm_vocab_f32": 33042176}
+NCU_TRAFFIC_BYTES = {"llm_vocab_f32": 32997376}
 
 
 def algorithmic_bytes(rows, cols, dtype, k):
@@ -165,6 +165,8 @@ def run_reference(args, rank, world):
     rows, cols, dtype, k, inv_t = WORKLOADS[args.workload]
     x = make_inputs(args.workload, 1000, "cpu")[0]
     xa = to_oracle_array(x)
+    # every host thread, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = oracle.num_threads()
 
     def step():
@@ -258,7 +260,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
-    ap.add_argument("--graph-steps", type=int, default=64, help="steps captured in the CUDA graph that is replayed")
+    ap.add_argument("--graph-steps", type=int, default=256, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -270,7 +272,7 @@ def main():
         args.warmup = 1 if args.warmup is None else args.warmup
         run_reference(args, rank, world)
         return
-    args.steps = 2000 if args.steps is None else args.steps
+    args.steps = 2048 if args.steps is None else args.steps
     args.warmup = 20 if args.warmup is None else args.warmup
     if args.workload == "yolo_nms":
         run_nms(args, local_rank)
@@ -399,11 +401,18 @@ def main():
         from tests.util import ORACLE_DTYPE, to_oracle_array
 
         xa = to_oracle_array(host[0])
-        reps = 10
-        t0 = time.perf_counter()
-        for _ in range(reps):
+        oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+        # parity spot check: one more step on buffer 0, indices against the oracle, bit for bit
+        step(0, stream)
+        torch.cuda.synchronize()
+        _, want_idx = oracle.softmax_topk(xa, k, inv_t, dtype=ORACLE_DTYPE[dtype])
+        if not (indices.cpu().numpy() == want_idx).all():
+            raise SystemExit("bench.py: the GPU result differs from the oracle")
+        reps, t0 = 0, time.perf_counter()
+        while reps < 10 or time.perf_counter() - t0 < 2.0:  # a bounded sample: about 2 s on all cores
             oracle.softmax_topk(xa, k, inv_t, dtype=ORACLE_DTYPE[dtype], sum_mode=oracle.SUM_F32_SEQUENTIAL,
                                 full_sort=True)
+            reps += 1
         dt = (time.perf_counter() - t0) / reps
         cpu_baseline = {"value": rows / dt, "unit": "rows/s", "cores": oracle.num_threads(), "kind": "port",
                         "sample": f"{reps} passes over one batch of {rows} rows ({dt * reps:.1f} s wall): max -> exp -> "
