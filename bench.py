@@ -246,6 +246,65 @@ def run_nms(args, local_rank):
         "gpu_launches": per_step * steps}))
 
 
+def run_vocab_sharded(args, rank, local_rank, world):
+    """Side line: one batch whose columns are split over the ranks (strong scaling).  A step = partial
+    selection on the local column slice, all-gather of the per-row packets (NCCL), merge on every rank."""
+    import torch.distributed as dist
+
+    from vkop_b200 import sharded, workloads
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows, cols, dtype, k, inv_t = WORKLOADS[args.workload]
+    lo, hi = sharded.split_even(cols, world, rank)
+    # every rank draws its own slice (the values of a slice do not depend on the others)
+    slices = [workloads.spiked_normal(rows, hi - lo, max(1, 32 // world), 9.0, 1.5, 7000 + 100 * rank + b, dtype).to(dev)
+              for b in range(NBUF)]
+    op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev)
+    steps = min(args.steps, 500)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        op(slices[i % NBUF])
+    barrier()
+    # Launched from the host, step by step: capturing the NCCL collective into a CUDA graph hung a
+    # two-rank run on this pool (most likely the process group's watchdog thread touching CUDA during
+    # the capture), so no graph here.
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        op(slices[i % NBUF])
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    peak, peak_kind = measured_peak()
+    esz = slices[0].element_size()
+    nbytes = rows * cols * esz + rows * k * (esz + 4)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fused_softmax_topk_rows_per_s", "value": rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
+            "config": {"workload": args.workload, "rows": rows, "cols": cols, "cols_per_gpu": hi - lo, "k": k,
+                       "sharding": f"vocab x{world}", "exchange": "NCCL all-gather of per-row packets + merge kernel",
+                       "launch": "host",
+                       "packet_bytes_per_rank": rows * (4 + 2 * k) * 4,
+                       "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * (hi - lo) * esz >> 20} MiB per rank)"},
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / (peak * world), "traffic": None, "peak_kind": peak_kind}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -260,6 +319,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
+    ap.add_argument("--sharding", default="rows", choices=["rows", "vocab"],
+                    help="N > 1: rows = every rank its own batch (weak scaling, no collective); vocab = the columns of "
+                         "one batch split over the ranks, packets all-gathered and merged (strong scaling)")
     ap.add_argument("--graph-steps", type=int, default=256, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 
@@ -276,6 +338,9 @@ def main():
     args.warmup = 20 if args.warmup is None else args.warmup
     if args.workload == "yolo_nms":
         run_nms(args, local_rank)
+        return
+    if args.sharding == "vocab":
+        run_vocab_sharded(args, rank, local_rank, world)
         return
 
     from vkop_b200 import capi

@@ -858,8 +858,8 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     // together: a call takes about 64 CTAs, a whole row per CTA when there are that many rows, so
     // that rows need no merge at all.  A call that waits for its predecessor spreads over all SMs.
     const bool overlapping = (d.flags & VKOP_FLAG_INPUT_READY) != 0;
-    if (d.rows <= slots / 2 || overlapping) {
-        int64_t s = slots / d.rows > 0 ? slots / d.rows : 1;
+    if (d.rows <= slots / 2) {  // (with more rows than that, byte-balanced ranges were measured faster than a CTA per row)
+        int64_t s = slots / d.rows;
         if (overlapping) {
             const int64_t few = (64 + d.rows - 1) / d.rows;
             s = few < s ? few : s;
