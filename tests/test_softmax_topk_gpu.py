@@ -289,6 +289,38 @@ def test_stream_back_to_back_with_input_ready(capi):
     assert torch.equal(o[1], ref[2][1])
 
 
+@pytest.mark.parametrize("rows,cols,k,dtype", [(16, 128256, 50, torch.float32),   # four parts per row, scratch lists
+                                               (5, 300007, 64, torch.float32),    # many parts, odd length
+                                               (64, 70001, 8, torch.float16),     # whole rows, 16-bit
+                                               (200, 40000, 32, torch.bfloat16),  # more rows than CTA pairs: CTAs cross rows
+                                               (1, 1 << 20, 16, torch.float32)])  # one long row
+def test_stream_overlapping_calls_in_every_launch_shape(capi, rows, cols, k, dtype):
+    """Back-to-back calls that may overlap (the caller vouches for the logits), one workspace, one output
+    buffer: every call's result must be intact when the next one is enqueued behind it."""
+    g = torch.Generator().manual_seed(rows * 7 + k)
+    xs = [torch.randn(rows, cols, generator=g).to(dtype) for _ in range(3)]
+    xg = [x.cuda() for x in xs]
+    want = [util.oracle_softmax_topk(x, k, 1.25) for x in xs]
+    d = capi.make_desc(xg[0], k, 1.25, path=capi.PATH_STREAM, flags=capi.FLAG_INPUT_READY)
+    ws = capi.Workspace(capi.softmax_topk_workspace_bytes(d))
+    outs = [(torch.empty((rows, k), dtype=dtype, device="cuda"), torch.empty((rows, k), dtype=torch.int32, device="cuda"))
+            for _ in xs]
+    for rep in range(12):
+        for x, o in zip(xg, outs):
+            capi.softmax_topk(x, k, 1.25, workspace=ws, out=o, path=capi.PATH_STREAM, flags=capi.FLAG_INPUT_READY)
+    torch.cuda.synchronize()
+    for o, (wv, wi) in zip(outs, want):
+        util.assert_indices_equal(o[1], wi, f"overlapping {rows}x{cols}")
+        util.assert_probs_close(o[0], wv, dtype, f"overlapping {rows}x{cols}")
+    # one output buffer for all calls: the last call's result stands
+    o = outs[0]
+    for rep in range(6):
+        for x in xg:
+            capi.softmax_topk(x, k, 1.25, workspace=ws, out=o, path=capi.PATH_STREAM, flags=capi.FLAG_INPUT_READY)
+    torch.cuda.synchronize()
+    util.assert_indices_equal(o[1], want[2][1], f"overlapping, shared output {rows}x{cols}")
+
+
 def test_stream_raw_smallest_and_packets(capi):
     g = torch.Generator().manual_seed(53)
     x = torch.randn(40, 70001, generator=g)

@@ -112,6 +112,26 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = p.k;
+    // ---- short lists (the usual case behind a tight threshold): the rank of a candidate is the number
+    // of candidates that beat it; PER threads share the count of one candidate.  No sort, no barrier. ----
+    constexpr int kSmall = 128;
+    if (n <= kSmall) {
+        constexpr int PER = THREADS / kSmall >= 1 ? THREADS / kSmall : 1;
+        static_assert(PER <= 32 && (PER & (PER - 1)) == 0, "a power of two within a warp");
+        for (int c0 = 0; c0 < kSmall; c0 += THREADS / PER) {
+            const int c = c0 + tid / PER, sub = tid % PER;
+            const uint64_t me = c < n ? list[c] : ~0ull;
+            int beat = 0;
+            for (int i = sub; i < n; i += PER)
+                beat += list[i] > me ? 1 : 0;
+#pragma unroll
+            for (int o = 1; o < PER; o <<= 1)
+                beat += __shfl_xor_sync(kFullMask, beat, o);
+            if (c < n && sub == 0 && beat < k)
+                emit<T>(p, row, beat, me, M, S, list_out);
+        }
+        return;
+    }
     // ---- narrow: r-th largest key of every full group of 32, minimised over the groups; the survivors
     // are regrouped and narrowed again while that still removes a good share of them ----
     uint64_t *src = list;
