@@ -262,7 +262,7 @@ def run_vocab_sharded(args, rank, local_rank, world):
     # every rank draws its own slice (the values of a slice do not depend on the others)
     slices = [workloads.spiked_normal(rows, hi - lo, max(1, 32 // world), 9.0, 1.5, 7000 + 100 * rank + b, dtype).to(dev)
               for b in range(NBUF)]
-    op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev)
+    op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev, exchange=args.exchange)
     steps = min(args.steps, 500)
 
     def barrier():
@@ -295,13 +295,17 @@ def run_vocab_sharded(args, rank, local_rank, world):
             "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
             "config": {"workload": args.workload, "rows": rows, "cols": cols, "cols_per_gpu": hi - lo, "k": k,
-                       "sharding": f"vocab x{world}", "exchange": "NCCL all-gather of per-row packets + merge kernel",
+                       "sharding": f"vocab x{world}", "exchange": ("NCCL all-gather of per-row packets" if args.exchange == "nccl" or world == 1
+                                    else "stores into peer memory + flags (NVLink)") + " + merge kernel",
                        "launch": "host",
                        "packet_bytes_per_rank": rows * (4 + 2 * k) * 4,
                        "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * (hi - lo) * esz >> 20} MiB per rank)"},
             "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
                          "frac": nbytes / (ms * 1e-3) / 1e9 / (peak * world), "traffic": None, "peak_kind": peak_kind}}))
     if world > 1:
+        if op.peer is not None:
+            dist.barrier()
+            op.peer.close()
         dist.destroy_process_group()
 
 
@@ -322,6 +326,8 @@ def main():
     ap.add_argument("--sharding", default="rows", choices=["rows", "vocab"],
                     help="N > 1: rows = every rank its own batch (weak scaling, no collective); vocab = the columns of "
                          "one batch split over the ranks, packets all-gathered and merged (strong scaling)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="--sharding vocab: how the packets travel (NCCL all-gather, or stores into peer memory)")
     ap.add_argument("--graph-steps", type=int, default=256, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 

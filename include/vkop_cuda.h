@@ -145,6 +145,30 @@ int vkop_cuda_softmax_topk_partial(const vkop_softmax_topk_desc *desc, const voi
 int vkop_cuda_softmax_topk_merge(const vkop_softmax_topk_desc *desc, const void *packets, int32_t shards,
                                  void *out_values, void *out_indices, void *stream);
 
+/* Packet exchange over peer memory instead of an all-gather (no counterpart in
+ * the reference, which is single-device).  Every rank owns a receive buffer
+ * `slots` of 2 * world * packets_bytes bytes and `flags` of 2 * world uint32,
+ * both zeroed once and mapped into every peer's address space (CUDA IPC or
+ * symmetric memory; peer access enabled).  Step `seq` (1, 2, 3, ... on every
+ * rank alike) uses half seq & 1 of both.
+ *
+ * vkop_cuda_packets_push stores this rank's packets (the output of `partial`)
+ * into slot [seq & 1][rank] of every rank's buffer -- peer_slots / peer_flags
+ * are DEVICE arrays of `world` device pointers, entry p being rank p's buffer --
+ * and then sets flag [seq & 1][rank] there to seq.  `tickets`: world uint32
+ * in local device memory, zeroed once.
+ *
+ * vkop_cuda_packets_wait makes the stream wait until the flags of all ranks
+ * in the LOCAL buffer show seq; `merge` on slots + (seq & 1) * world *
+ * packets_bytes follows it on the same stream.  The wait is bounded: after
+ * max_polls looks (about a microsecond each) it writes VKOP_TIMEOUT to
+ * *status (device memory, set to VKOP_OK by the caller beforehand) and lets
+ * the stream go on; read the status after synchronising. */
+int vkop_cuda_packets_push(const void *packets, size_t packets_bytes, void *const *peer_slots, void *const *peer_flags,
+                           int32_t rank, int32_t world, uint32_t seq, void *tickets, void *stream);
+int vkop_cuda_packets_wait(const void *flags, int32_t world, uint32_t seq, uint32_t max_polls, int32_t *status,
+                           void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* NMS (ONNX NonMaxSuppression) per (batch, class).
  *

@@ -1,4 +1,5 @@
-"""Vocabulary-sharded Softmax + TopK on two or more GPUs (NCCL): one process per GPU."""
+"""Vocabulary-sharded Softmax + TopK on two or more GPUs: one process per GPU; the packets travel either
+through an NCCL all-gather or by stores into peer memory."""
 from __future__ import annotations
 
 import os
@@ -17,7 +18,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, q):
+def _worker(rank: int, world: int, port: int, q, exchange: str = "nccl"):
     import torch.distributed as dist
 
     import oracle
@@ -34,25 +35,43 @@ def _worker(rank: int, world: int, port: int, q):
         x = workloads.sharded_vocab(rows=64, cols=256000)
         lo, hi = split_even(x.shape[1], world, rank)
         shard = x[:, lo:hi].contiguous().cuda()
-        op = VocabShardedSoftmaxTopk(64, hi - lo, lo, 64, x.dtype)
+        op = VocabShardedSoftmaxTopk(64, hi - lo, lo, 64, x.dtype, exchange=exchange)
         v, i = op(shard)
+        v, i = v.clone(), i.clone()
         v2, i2 = op(shard)  # scratch is reusable
+        v2, i2 = v2.clone(), i2.clone()
+        # other logits in between and many steps back to back: the receive buffers are two steps deep
+        y = workloads.sharded_vocab(rows=64, cols=256000, seed=77)
+        yshard = y[:, lo:hi].contiguous().cuda()
+        for _ in range(9):
+            op(yshard)
+            op(shard)
+        vy, iy = op(yshard)
         torch.cuda.synchronize()
         wv, wi = util.oracle_softmax_topk(x, 64)
+        wvy, wiy = util.oracle_softmax_topk(y, 64)
         ok = True
         try:
             util.assert_indices_equal(i, wi, f"rank {rank}")
             util.assert_probs_close(v, wv, x.dtype, f"rank {rank}")
             assert torch.equal(i, i2) and torch.equal(v, v2)
+            util.assert_indices_equal(iy, wiy, f"rank {rank}, second input")
+            util.assert_probs_close(vy, wvy, x.dtype, f"rank {rank}, second input")
+            if op.peer is not None:
+                assert not op.peer.timed_out()
         except AssertionError as e:
             ok = str(e)
         q.put((rank, ok))
+        if op.peer is not None:
+            dist.barrier()  # no rank unmaps while another may still store into its memory
+            op.peer.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_vocab_sharded_nccl(world):
+def test_vocab_sharded(world, exchange):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -60,7 +79,7 @@ def test_vocab_sharded_nccl(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
@@ -68,3 +87,57 @@ def test_vocab_sharded_nccl(world):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(r[1] is True for r in results), results
+
+
+def test_packet_wait_gives_up_with_a_status():
+    """A flag that nobody sets: the bounded wait returns VKOP_TIMEOUT in the status word and the context
+    stays usable (no trap, no hang)."""
+    from vkop_b200 import capi
+
+    flags = torch.zeros((2, 4), dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    capi.packets_wait(flags, 4, 1, status, max_polls=2000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == -5
+    # flags that are set let it through
+    flags[1, :] = 3
+    status.zero_()
+    capi.packets_wait(flags, 4, 3, status, max_polls=2000)
+    x = torch.randn(4, 1000, device="cuda")
+    v, i = capi.softmax_topk(x, 5)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and i.shape == (4, 5)
+
+
+def test_peer_exchange_kernels_with_emulated_ranks():
+    """The push / wait / merge sequence of four ranks, emulated in one process on one GPU: every "rank" has its
+    own receive buffer and flags, the pointer tables name all of them, and the kernels of the ranks run one
+    after the other on one stream (so no kernel ever waits for a kernel that has not run)."""
+    import oracle
+    from tests import util
+    from vkop_b200 import capi, workloads
+    from vkop_b200.sharded import split_even
+
+    world, rows, k = 4, 48, 64
+    words = capi.packet_bytes(k) // 4
+    dev = torch.device("cuda")
+    slots = [torch.zeros((2, world, rows, words), dtype=torch.int32, device=dev) for _ in range(world)]
+    flags = [torch.zeros((2, world), dtype=torch.int32, device=dev) for _ in range(world)]
+    tickets = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    slot_ptrs = torch.tensor([t.data_ptr() for t in slots], dtype=torch.int64, device=dev)
+    flag_ptrs = torch.tensor([t.data_ptr() for t in flags], dtype=torch.int64, device=dev)
+    for seq in range(1, 6):
+        x = workloads.sharded_vocab(rows=rows, cols=100000, seed=seq)
+        for r in range(world):
+            lo, hi = split_even(x.shape[1], world, r)
+            packets = capi.softmax_topk_partial(x[:, lo:hi].contiguous().cuda(), k, lo)
+            capi.packets_push(packets, slot_ptrs, flag_ptrs, r, world, seq, tickets[r])
+        wv, wi = util.oracle_softmax_topk(x, k)
+        for r in range(world):
+            capi.packets_wait(flags[r], world, seq, status, max_polls=1000)
+            v, i = capi.softmax_topk_merge(slots[r][seq & 1], rows, k, x.dtype)
+            util.assert_indices_equal(i, wi, f"emulated rank {r}, step {seq}")
+            util.assert_probs_close(v, wv, x.dtype, f"emulated rank {r}, step {seq}")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0

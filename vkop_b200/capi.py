@@ -27,6 +27,7 @@ EXPORTS = [
     "vkop_cuda_packet_bytes", "vkop_cuda_softmax_topk_partial", "vkop_cuda_softmax_topk_merge",
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
     "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
+    "vkop_cuda_packets_push", "vkop_cuda_packets_wait",
 ]
 
 
@@ -78,6 +79,8 @@ def lib() -> C.CDLL:
         L.vkop_cuda_softmax_topk_merge.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, C.c_int32, vp, vp, vp]
         L.vkop_cuda_nms_workspace.argtypes = [C.POINTER(NmsDesc), C.POINTER(sz)]
         L.vkop_cuda_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, vp, sz, vp]
+        L.vkop_cuda_packets_push.argtypes = [vp, sz, vp, vp, C.c_int32, C.c_int32, C.c_uint32, vp, vp]
+        L.vkop_cuda_packets_wait.argtypes = [vp, C.c_int32, C.c_uint32, C.c_uint32, vp, vp]
         L.vkop_cuda_static_scratch_bytes.restype = sz
         L.vkop_cuda_softmax_topk_static.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp]
         _lib = L
@@ -162,6 +165,17 @@ def softmax_topk(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, ind
     check(fn(C.byref(desc), logits.data_ptr(), values.data_ptr(), indices.data_ptr(), workspace.ptr,
              workspace.buf.numel(), _stream()), "topk" if standalone_topk else "softmax_topk")
     return values, indices
+
+
+def packets_push(packets: torch.Tensor, peer_slots: torch.Tensor, peer_flags: torch.Tensor, rank: int, world: int,
+                 seq: int, tickets: torch.Tensor) -> None:
+    """peer_slots / peer_flags: int64 CUDA tensors holding one device pointer per rank."""
+    check(lib().vkop_cuda_packets_push(packets.data_ptr(), packets.numel() * packets.element_size(), peer_slots.data_ptr(),
+                                       peer_flags.data_ptr(), rank, world, seq, tickets.data_ptr(), _stream()), "packets_push")
+
+
+def packets_wait(flags: torch.Tensor, world: int, seq: int, status: torch.Tensor, max_polls: int = 1 << 20) -> None:
+    check(lib().vkop_cuda_packets_wait(flags.data_ptr(), world, seq, max_polls, status.data_ptr(), _stream()), "packets_wait")
 
 
 def static_scratch_bytes() -> int:

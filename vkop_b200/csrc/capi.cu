@@ -235,6 +235,22 @@ int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scor
     return launch_nms(*desc, boxes, scores, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream));
 }
 
+int vkop_cuda_packets_push(const void *packets, size_t packets_bytes, void *const *peer_slots, void *const *peer_flags,
+                           int32_t rank, int32_t world, uint32_t seq, void *tickets, void *stream) {
+    if (!packets || !peer_slots || !peer_flags || !tickets || world < 1 || world > 1024 || rank < 0 || rank >= world ||
+        seq == 0 || packets_bytes % 4 != 0)
+        return VKOP_INVALID_ARG;
+    return launch_packets_push(packets, packets_bytes, peer_slots, peer_flags, rank, world, seq, tickets,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int vkop_cuda_packets_wait(const void *flags, int32_t world, uint32_t seq, uint32_t max_polls, int32_t *status,
+                           void *stream) {
+    if (!flags || !status || world < 1 || world > 1024 || seq == 0 || max_polls == 0)
+        return VKOP_INVALID_ARG;
+    return launch_packets_wait(flags, world, seq, max_polls, status, static_cast<cudaStream_t>(stream));
+}
+
 // ---------------------------------------------------------------------------
 // Fused Softmax + TopK without a caller workspace.
 //

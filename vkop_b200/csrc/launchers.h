@@ -63,4 +63,9 @@ int plan_nms(const vkop_nms_desc &d, size_t *bytes);
 int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, int32_t *out_rows, int32_t *out_count,
                void *workspace, cudaStream_t stream);
 
+// ---- packet exchange over peer memory (peer_exchange.cu) ----
+int launch_packets_push(const void *packets, size_t bytes, void *const *peer_slots, void *const *peer_flags, int rank,
+                        int world, uint32_t seq, void *tickets, cudaStream_t stream);
+int launch_packets_wait(const void *flags, int world, uint32_t seq, uint32_t max_polls, int *status, cudaStream_t stream);
+
 }  // namespace vkop_cuda
