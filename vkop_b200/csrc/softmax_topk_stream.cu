@@ -1,43 +1,39 @@
-// Fused Softmax + TopK, streaming path: the kernels for large batches.
+// Fused Softmax + TopK, streaming path: one kernel for large batches.
 //
-// Kernel 1 (stream).  A fixed grid of CTAs, all resident at once (two per SM),
-// splits the whole [rows, cols] tensor by bytes.  Every CTA owns one contiguous
-// range of 16-byte vector slots; range boundaries are snapped to multiples of
-// 256 vectors inside a row, so that a CTA never holds a sliver of a row, and
-// with few rows every row is cut into the same number of CTAs and no CTA
-// crosses a row.  A CTA walks its range in tiles that are staged through
-// shared memory with cp.async, two stages deep: the copy of the next tile is
-// in flight while the current one is processed, every thread copies into and
-// reads back its own slots only, and the only wait is the hardware wait on the
-// thread's own copy groups (no spin-wait anywhere).
+// Streaming.  Every CTA owns one contiguous range of 16-byte vector slots of the [rows, cols]
+// tensor: a whole row, one of a few equal parts of a row, or (with more rows than CTA slots) a
+// byte-balanced range that may run across rows, its boundaries snapped to multiples of 256 vectors
+// inside a row so that no CTA holds a sliver.  A CTA walks its range in tiles that are staged
+// through shared memory with cp.async, two stages deep: the copy of the next tile is in flight
+// while the current one is processed, every thread copies into and reads back its own slots only,
+// and the only wait is the hardware wait on the thread's own copy groups (no spin-wait anywhere).
 //
-// Per tile and thread: the maximum of its elements updates a running maximum
-// m_t and rescales a running exp-sum s_t (online softmax).  The running thread
-// maxima give the selection threshold T: lanes form groups so that there are
-// at least k groups, and T is the smallest group maximum, so at least k
-// elements of the part reach T.  T is refreshed on tiles 0, 1, 3, 7, ... of a
-// part (one barrier each; it settles quickly and only rises inside a part).
-// An element >= T is kept: every thread owns a few private slots in shared
-// memory and appends there with a plain predicated store -- no atomic and no
-// divergent path on the common route; a thread whose slots are full appends
-// to a small shared overflow list instead.
+// Per tile and thread: the maximum of its elements updates a running maximum m_t and rescales a
+// running exp-sum s_t (online softmax).  The running thread maxima give the selection threshold T
+// (stream_refresh_threshold): any value that at least k thread maxima reach is a lower bound of the
+// k-th largest element; T is refreshed on tiles 0, 1, 3, 7, ... of a part and only rises inside a
+// part.  An element >= T is kept: every thread owns a few private slots in shared memory and appends
+// there with a plain store; a thread whose slots are full appends to a shared overflow list.
 //
-// When a CTA leaves a row (or its range ends) it finishes that row part: the
-// statistics are reduced over the CTA, candidates below the final threshold
-// are dropped, and the part is published to global scratch with plain stores.
-// The CTA then streams on or retires; it never waits for another CTA.
+// End of a row part (stream_finish_part): the statistics are reduced over the CTA, candidates below
+// the final threshold are dropped, and then, by launch shape:
+//   whole rows   the CTA selects the k best of its candidates and writes the result;
+//   cluster      the CTAs of a row are a thread-block cluster: cluster barrier, then the first CTA
+//                reads the other CTAs' lists through distributed shared memory, merges and writes;
+//   otherwise    the part is published to scratch memory; the last part of the row to arrive
+//                (ticket counter) gathers the lists of the row, merges and writes.
+// A CTA never waits for another CTA of its own launch except at the cluster barrier.
 //
-// Kernel 2 (select), one light CTA per row, gathers the parts of its row,
-// merges their statistics and selects the k best (select.cuh).
-//
-// Both kernels are launched with programmatic stream serialization.  Each lets
-// its successor start early (griddepcontrol.launch_dependents on entry) and
-// waits for its predecessor (griddepcontrol.wait) before it touches memory the
-// predecessor may still use: the select kernel at once, the stream kernel
-// before it reads the logits -- or, when the caller states that the logits were
-// complete before the call, only before its first write to scratch memory.
-// Back-to-back calls then overlap: while the select kernel of one call works,
-// the stream kernel of the next call already pulls its logits from HBM.
+// Launches use programmatic stream serialization.  A kernel lets its successor in as soon as all
+// its CTAs run (griddepcontrol.launch_dependents) and orders itself against its predecessor only
+// where memory demands it.  Without VKOP_FLAG_INPUT_READY that is at once (griddepcontrol.wait before
+// the first read).  With the flag the logits need no ordering, and what remains is: scratch lists
+// alternate between two sets by call parity, so a call only needs the call before its predecessor
+// to be done with a row's lists; and results of one row are written in call order.  Both are
+// checked with one acquire load of a per-row counter of finished calls; only when the check fails
+// does the CTA fall back to griddepcontrol.wait for the whole previous call.  Calls number
+// themselves on the device (an arrival ticket per CTA, drawn before the successor is let in), so a
+// replayed CUDA graph needs no changing parameter.  Back-to-back calls then overlap several deep.
 #include "common.cuh"
 #include "launchers.h"
 #include "select.cuh"
