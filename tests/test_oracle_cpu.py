@@ -189,6 +189,36 @@ def test_workspace_planning_needs_no_device():
     assert capi.lib().vkop_cuda_softmax_topk_workspace(ctypes.byref(d), ctypes.byref(n)) == capi.INVALID_ARG
 
 
+def test_planner_serves_every_shape_and_flag_without_a_device():
+    """The planners are host code: sweep shapes, element types, k, paths and the overlap flag, and check that
+    every supported combination gets a finite scratch size and every refusal is a status, not a crash."""
+    from vkop_b200 import capi
+    n = ctypes.c_size_t()
+    fn = capi.lib().vkop_cuda_softmax_topk_workspace
+    served = 0
+    for rows in (1, 2, 5, 16, 64, 148, 149, 300, 512, 4096, 100000):
+        for cols in (1, 7, 1000, 16384, 32000, 128256, 256000, 300007, 1 << 20, 1 << 24):
+            if rows * cols > (1 << 34):
+                continue
+            for dtype in (capi.F32, capi.F16, capi.BF16):
+                for k in (1, 5, 50, 64, 128, 300, 1024):
+                    if k > cols:
+                        continue
+                    for path in (capi.PATH_AUTO, capi.PATH_CHUNK, capi.PATH_STREAM, capi.PATH_RADIX):
+                        for flags in (0, capi.FLAG_INPUT_READY):
+                            d = capi.SoftmaxTopkDesc(rows=rows, cols=cols, row_stride=cols, dtype=dtype, k=k,
+                                                     index_dtype=capi.I32, value_kind=0, inv_temperature=1.0, largest=1,
+                                                     path=path, splits=0, index_offset=0, flags=flags, reserved=0)
+                            rc = fn(ctypes.byref(d), ctypes.byref(n))
+                            assert rc in (capi.OK, capi.UNSUPPORTED), (rows, cols, dtype, k, path, flags, rc)
+                            if rc == capi.OK:
+                                served += 1
+                                assert 0 <= n.value < (64 << 30), (rows, cols, k, path, n.value)
+                            if path == capi.PATH_AUTO:
+                                assert rc == capi.OK, ("the automatic choice must serve", rows, cols, dtype, k, flags)
+    assert served > 5000
+
+
 def test_product_has_no_cpu_path():
     from vkop_b200 import capi
     x = torch.randn(2, 100)
