@@ -898,9 +898,8 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
     // one arrival counter for the workspace; per row: an arrival counter for each of the two sets of
-    // lists and the number of calls that have written the row's result (scratch lists), turns drawn
-    // and turns finished (clusters)
-    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 5 * 4 + 255) / 256) * 256;
+    // lists and the number of calls that have written the row's result
+    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 3 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
     plan->smem_bytes = 2 * static_cast<size_t>(threads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamSlots) * threads * 8;
     return VKOP_OK;
