@@ -196,6 +196,17 @@ int vkop_cuda_nms_workspace(const vkop_nms_desc *desc, size_t *bytes);
 int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scores, int32_t *out_rows,
                   int32_t *out_count, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same NMS straight on a detection head as a YOLO-style model emits it:
+ * head [B, 4 + C, N] fp32, planes 0-3 the box coordinates (cx, cy, w, h with
+ * center_point_box = 1), planes 4.. the class scores.  Nothing is transposed
+ * or copied: the score planes are scanned where they lie and the boxes of the
+ * surviving candidates are gathered from the four coordinate planes.  Stands
+ * in for the CPU post-processing of example/yolo/main.cpp:60-179 (which reads
+ * the head back and runs argmax + NMS on the host) in its per-class form.
+ * Same descriptor, workspace and outputs as vkop_cuda_nms. */
+int vkop_cuda_yolo_nms(const vkop_nms_desc *desc, const void *head, int32_t *out_rows, int32_t *out_count,
+                       void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* Fused Softmax + TopK that needs no workspace from the caller and allocates
  * nothing: the chunk kernel works in a fixed array inside the loaded module

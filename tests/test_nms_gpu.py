@@ -124,3 +124,33 @@ def test_argument_errors(capi):
     d.num_boxes = -1
     assert L.vkop_cuda_nms_workspace(C.byref(d), C.byref(n)) == capi.INVALID_ARG
     assert L.vkop_cuda_nms(None, None, None, None, None, None, 0, None) == capi.INVALID_ARG
+
+
+def _head(boxes: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+    """The layout a YOLO-style detection head emits: [B, 4 + C, N], coordinate planes first."""
+    return torch.cat([boxes.transpose(1, 2), scores], dim=1).contiguous()
+
+
+@pytest.mark.parametrize("batch,classes,anchors", [(2, 12, 8400), (3, 5, 1001), (1, 1, 37), (16, 80, 8400)])
+def test_nms_on_the_detection_head_in_place(capi, batch, classes, anchors):
+    """vkop_cuda_yolo_nms reads boxes and scores where the head holds them; the result must be the rows
+    vkop_cuda_nms gives on the separate tensors, which the oracle pins."""
+    boxes, scores = workloads.yolo_detect(seed=21, batch=batch, classes=classes, anchors=anchors)
+    kw = dict(workloads.YOLO_PARAMS)
+    if anchors < 300:
+        kw["pre_topk"] = 0
+    want_rows, want_total, _ = oracle.nms(boxes.numpy(), scores.numpy(), **kw)
+    rows, count = capi.yolo_nms(_head(boxes, scores).cuda(), **kw)
+    torch.cuda.synchronize()
+    n = int(count.item())
+    assert n == want_total
+    got = rows[:min(n, rows.shape[0])].cpu().numpy()
+    assert np.array_equal(got, want_rows[:got.shape[0]])
+    # an odd offset of the head inside its buffer: the score planes no longer start on 16 bytes
+    buf = torch.zeros(_head(boxes, scores).numel() + 3)
+    buf[1:-2] = _head(boxes, scores).flatten()
+    shifted = buf.cuda()[1:-2].view(batch, 4 + classes, anchors)
+    rows2, count2 = capi.yolo_nms(shifted, **kw)
+    torch.cuda.synchronize()
+    assert int(count2.item()) == want_total
+    assert np.array_equal(rows2[:got.shape[0]].cpu().numpy(), got)

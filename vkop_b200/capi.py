@@ -27,7 +27,7 @@ EXPORTS = [
     "vkop_cuda_packet_bytes", "vkop_cuda_softmax_topk_partial", "vkop_cuda_softmax_topk_merge",
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
     "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
-    "vkop_cuda_packets_push", "vkop_cuda_packets_wait",
+    "vkop_cuda_packets_push", "vkop_cuda_packets_wait", "vkop_cuda_yolo_nms",
 ]
 
 
@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
         L.vkop_cuda_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_packets_push.argtypes = [vp, sz, vp, vp, C.c_int32, C.c_int32, C.c_uint32, vp, vp]
         L.vkop_cuda_packets_wait.argtypes = [vp, C.c_int32, C.c_uint32, C.c_uint32, vp, vp]
+        L.vkop_cuda_yolo_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_static_scratch_bytes.restype = sz
         L.vkop_cuda_softmax_topk_static.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp]
         _lib = L
@@ -165,6 +166,35 @@ def softmax_topk(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, ind
     check(fn(C.byref(desc), logits.data_ptr(), values.data_ptr(), indices.data_ptr(), workspace.ptr,
              workspace.buf.numel(), _stream()), "topk" if standalone_topk else "softmax_topk")
     return values, indices
+
+
+def yolo_nms(head: torch.Tensor, center_point_box: int = 1, max_output_boxes_per_class: int = 0,
+             iou_threshold: float = 0.0, score_threshold: float = 0.0, pre_topk: int = 0, capacity_rows: int | None = None,
+             workspace: Workspace | None = None, out=None):
+    """NMS on a detection head [B, 4 + C, N] (coordinate planes, then score planes), read in place.
+    Returns (rows int32 [capacity, 3], count int32 [1]) like nms()."""
+    if not head.is_cuda:
+        raise RuntimeError("vkop_b200 runs on CUDA device memory only")
+    assert head.dtype == torch.float32 and head.dim() == 3 and head.shape[1] > 4 and head.is_contiguous()
+    B, planes, N = head.shape
+    Cn = planes - 4
+    if capacity_rows is None:
+        per = max_output_boxes_per_class if max_output_boxes_per_class > 0 else (pre_topk if pre_topk > 0 else N)
+        capacity_rows = B * Cn * min(per, N)
+    desc = NmsDesc(num_batch=B, num_class=Cn, num_boxes=N, center_point_box=center_point_box,
+                   max_output_boxes_per_class=max_output_boxes_per_class, pre_topk=pre_topk,
+                   iou_threshold=iou_threshold, score_threshold=score_threshold, capacity_rows=capacity_rows)
+    need = nms_workspace_bytes(desc)
+    if workspace is None or workspace.nbytes < need:
+        workspace = Workspace(need, head.device)
+    if out is None:
+        rows = torch.empty((max(capacity_rows, 1), 3), dtype=torch.int32, device=head.device)
+        count = torch.empty(1, dtype=torch.int32, device=head.device)
+    else:
+        rows, count = out
+    check(lib().vkop_cuda_yolo_nms(C.byref(desc), head.data_ptr(), rows.data_ptr(), count.data_ptr(), workspace.ptr,
+                                   workspace.buf.numel(), _stream()), "yolo_nms")
+    return rows, count
 
 
 def packets_push(packets: torch.Tensor, peer_slots: torch.Tensor, peer_flags: torch.Tensor, rank: int, world: int,

@@ -235,6 +235,27 @@ int vkop_cuda_nms(const vkop_nms_desc *desc, const void *boxes, const void *scor
     return launch_nms(*desc, boxes, scores, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream));
 }
 
+int vkop_cuda_yolo_nms(const vkop_nms_desc *desc, const void *head, int32_t *out_rows, int32_t *out_count,
+                       void *workspace, size_t workspace_bytes, void *stream) {
+    if (!desc || !out_count)
+        return VKOP_INVALID_ARG;
+    size_t need = 0;
+    int rc = plan_nms(*desc, &need);
+    if (rc != VKOP_OK)
+        return rc;
+    const int64_t problems = static_cast<int64_t>(desc->num_batch) * desc->num_class;
+    if (problems > 0 && desc->num_boxes > 0 && !head)
+        return VKOP_INVALID_ARG;
+    if (desc->capacity_rows > 0 && !out_rows)
+        return VKOP_INVALID_ARG;
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return VKOP_WORKSPACE_TOO_SMALL;
+    // head [B, 4 + C, N]: four coordinate planes, then one score plane per class
+    const int64_t n = desc->num_boxes, plane = (4 + static_cast<int64_t>(desc->num_class)) * n;
+    const float *h = static_cast<const float *>(head);
+    return launch_nms(*desc, h, h + 4 * n, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream), plane, plane, n);
+}
+
 int vkop_cuda_packets_push(const void *packets, size_t packets_bytes, void *const *peer_slots, void *const *peer_flags,
                            int32_t rank, int32_t world, uint32_t seq, void *tickets, void *stream) {
     if (!packets || !peer_slots || !peer_flags || !tickets || world < 1 || world > 1024 || rank < 0 || rank >= world ||

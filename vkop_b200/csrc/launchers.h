@@ -60,8 +60,11 @@ int launch_softmax(const vkop_softmax_desc &d, const void *input, void *output, 
 
 // ---- NMS (nms.cu) ----
 int plan_nms(const vkop_nms_desc &d, size_t *bytes);
+// Strides 0: dense [B, N, 4] boxes and [B, C, N] scores.  Otherwise: elements between the score blocks /
+// the boxes of consecutive batches, and between the four coordinate planes of a box.
 int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, int32_t *out_rows, int32_t *out_count,
-               void *workspace, cudaStream_t stream);
+               void *workspace, cudaStream_t stream, int64_t score_bstride = 0, int64_t box_bstride = 0,
+               int64_t box_cstride = 0);
 
 // ---- packet exchange over peer memory (peer_exchange.cu) ----
 int launch_packets_push(const void *packets, size_t bytes, void *const *peer_slots, void *const *peer_flags, int rank,

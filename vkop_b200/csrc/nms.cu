@@ -30,8 +30,11 @@ constexpr int kNmsMaxSorted = 4096;  // candidates one problem can order in shar
 constexpr int kNmsMaskMax = 512;     // problems up to this many ordered boxes use the bit-mask sweep
 
 struct NmsParams {
-    const float *boxes;   // [B, N, 4]
+    const float *boxes;   // [B, N, 4], or one component plane per coordinate (box_cstride > 0)
     const float *scores;  // [B, C, N]
+    int64_t score_bstride;  // elements between the score blocks of consecutive batches (C * N when dense)
+    int64_t box_bstride;    // elements between the boxes of consecutive batches
+    int64_t box_cstride;    // 0: a box is 4 consecutive floats; else the distance between its coordinates
     int B, C, N;
     int center_point_box, max_out, pre_topk;
     float iou_thr, score_thr;
@@ -150,8 +153,8 @@ __global__ void __launch_bounds__(kNmsThreads) nms_problem_kernel(const NmsParam
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int prob = blockIdx.x;
     const int b = prob / p.C;
-    const float *srow = p.scores + static_cast<int64_t>(prob) * p.N;
-    const float *brow = p.boxes + static_cast<int64_t>(b) * p.N * 4;
+    const float *srow = p.scores + static_cast<int64_t>(b) * p.score_bstride + static_cast<int64_t>(prob - b * p.C) * p.N;
+    const float *brow = p.boxes + static_cast<int64_t>(b) * p.box_bstride;
 
     if (tid == 0)
         s_count = 0;
@@ -217,7 +220,11 @@ __global__ void __launch_bounds__(kNmsThreads) nms_problem_kernel(const NmsParam
     // ---- boxes of the ordered candidates ----
     for (int i = tid; i < M; i += kNmsThreads) {
         const uint32_t idx = cand_idx(s_c[i]);
-        const float4 raw = *reinterpret_cast<const float4 *>(brow + static_cast<int64_t>(idx) * 4);
+        float4 raw;
+        if (p.box_cstride == 0)
+            raw = *reinterpret_cast<const float4 *>(brow + static_cast<int64_t>(idx) * 4);
+        else
+            raw = make_float4(brow[idx], brow[p.box_cstride + idx], brow[2 * p.box_cstride + idx], brow[3 * p.box_cstride + idx]);
         const BoxA bx = to_corners(raw, p.center_point_box);
         s_box[i] = bx;
         s_area[i] = box_area(bx);
@@ -385,12 +392,12 @@ int plan_nms(const vkop_nms_desc &d, size_t *bytes) {
 }
 
 int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, int32_t *out_rows, int32_t *out_count,
-               void *workspace, cudaStream_t stream) {
+               void *workspace, cudaStream_t stream, int64_t score_bstride, int64_t box_bstride, int64_t box_cstride) {
     NmsPlan pl;
     const int rc = make_plan(d, &pl);
     if (rc != VKOP_OK)
         return rc;
-    if (reinterpret_cast<uintptr_t>(boxes) % 16 != 0 || reinterpret_cast<uintptr_t>(scores) % 4 != 0)
+    if (reinterpret_cast<uintptr_t>(boxes) % (box_cstride == 0 ? 16 : 4) != 0 || reinterpret_cast<uintptr_t>(scores) % 4 != 0)
         return VKOP_INVALID_ARG;
     const int64_t problems = static_cast<int64_t>(d.num_batch) * d.num_class;
     if (problems == 0 || d.num_boxes == 0) {
@@ -403,6 +410,9 @@ int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, in
     NmsParams p;
     p.boxes = reinterpret_cast<const float *>(boxes);
     p.scores = reinterpret_cast<const float *>(scores);
+    p.score_bstride = score_bstride > 0 ? score_bstride : static_cast<int64_t>(d.num_class) * d.num_boxes;
+    p.box_bstride = box_bstride > 0 ? box_bstride : static_cast<int64_t>(d.num_boxes) * 4;
+    p.box_cstride = box_cstride;
     p.B = d.num_batch;
     p.C = d.num_class;
     p.N = d.num_boxes;
