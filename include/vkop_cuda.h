@@ -145,6 +145,18 @@ int vkop_cuda_softmax_topk_partial(const vkop_softmax_topk_desc *desc, const voi
 int vkop_cuda_softmax_topk_merge(const vkop_softmax_topk_desc *desc, const void *packets, int32_t shards,
                                  void *out_values, void *out_indices, void *stream);
 
+/* Sampling tail over the k survivors of vkop_cuda_softmax_topk (no counterpart
+ * in the reference: the step that follows top-k in a vocabulary-selection
+ * path).  values [rows, k] are the probabilities as the operator wrote them
+ * (best first), indices [rows, k] their columns, u [rows] uniform numbers in
+ * [0, 1) from the caller.  Per row, all sums sequential in fp32: the nucleus
+ * is the shortest prefix whose sum reaches top_p times the sum of all k
+ * (top_p >= 1 keeps all k); the choice is the first entry whose prefix sum
+ * exceeds u times the nucleus' sum.  out_choice [rows] receives the position
+ * (0 .. k-1), out_token [rows] (same type as indices) the column. */
+int vkop_cuda_sample_topk(const void *values, int32_t dtype, const void *indices, int32_t index_dtype, int64_t rows,
+                          int32_t k, float top_p, const float *u, int32_t *out_choice, void *out_token, void *stream);
+
 /* Packet exchange over peer memory instead of an all-gather (no counterpart in
  * the reference, which is single-device).  Every rank owns a receive buffer
  * `slots` of 2 * world * packets_bytes bytes and `flags` of 2 * world uint32,

@@ -137,6 +137,22 @@ def merge_stats(m: np.ndarray, s: np.ndarray):
     return mo.value, so.value
 
 
+def sample_topk(values: np.ndarray, indices: np.ndarray, top_p: float, u: np.ndarray, dtype: int | None = None):
+    """Sampling tail over the k survivors per row.  Returns (choice int32 [rows], token int64 [rows])."""
+    dt = dtype_of(values, dtype)
+    v = np.ascontiguousarray(_as_storage(values, dt))
+    idx = np.ascontiguousarray(indices, np.int64)
+    uu = np.ascontiguousarray(u, np.float32)
+    rows, k = v.shape
+    choice = np.empty(rows, np.int32)
+    token = np.empty(rows, np.int64)
+    rc = lib().oracle_sample_topk(_ptr(v), C.c_int(dt), _ptr(idx), C.c_int64(rows), C.c_int(k), C.c_float(top_p), _ptr(uu),
+                                  _ptr(choice), _ptr(token))
+    if rc != 0:
+        raise ValueError("oracle_sample_topk: bad argument")
+    return choice, token
+
+
 def nms(boxes: np.ndarray, scores: np.ndarray, center_point_box: int = 0, max_output_boxes_per_class: int = 0,
         iou_threshold: float = 0.0, score_threshold: float = 0.0, pre_topk: int = 0, capacity_rows: int | None = None):
     """Returns (rows int32 [count,3], total count, per-(b,c) kept counts)."""

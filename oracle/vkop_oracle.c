@@ -696,6 +696,52 @@ int oracle_ref_nms_problem(const float *boxes_n4, const float *scores_n, int N, 
     return sel;
 }
 
+/* Sampling tail over the k survivors of one fused Softmax + TopK call (no counterpart in the
+ * reference; it is the step that follows top-k in a vocabulary-selection path).  Per row, with the
+ * probabilities p_0 >= p_1 >= ... as the operator emits them and all sums sequential in fp32:
+ *   total = sum of all k;  n = the smallest count whose prefix sum reaches top_p * total (n = k when
+ *   top_p >= 1);  mass = prefix sum of those n;  the choice is the first j < n whose prefix sum
+ *   exceeds u * mass (j = n - 1 if none does).
+ * out_choice[r] = j; out_token[r] = indices[r][j]. */
+int oracle_sample_topk(const void *values, int dtype, const int64_t *indices, int64_t rows, int k, float top_p,
+                       const float *u, int32_t *out_choice, int64_t *out_token) {
+    if (!values || !indices || !u || !out_choice || !out_token || rows < 0 || k < 1 || !(top_p > 0.0f))
+        return -1;
+    for (int64_t r = 0; r < rows; r++) {
+        float total = 0.0f;
+        for (int j = 0; j < k; j++)
+            total += load_elem(values, dtype, r * k + j);
+        int n = k;
+        if (top_p < 1.0f) {
+            const float want = top_p * total;
+            float acc = 0.0f;
+            for (int j = 0; j < k; j++) {
+                acc += load_elem(values, dtype, r * k + j);
+                if (acc >= want) {
+                    n = j + 1;
+                    break;
+                }
+            }
+        }
+        float mass = 0.0f;
+        for (int j = 0; j < n; j++)
+            mass += load_elem(values, dtype, r * k + j);
+        const float target = u[r] * mass;
+        int pick = n - 1;
+        float acc = 0.0f;
+        for (int j = 0; j < n; j++) {
+            acc += load_elem(values, dtype, r * k + j);
+            if (acc > target) {
+                pick = j;
+                break;
+            }
+        }
+        out_choice[r] = pick;
+        out_token[r] = indices[r * k + pick];
+    }
+    return 0;
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libvkop_cuda.so")
 SOURCES = ["capi.cu", "softmax_topk.cu", "softmax_topk_stream.cu", "radix_select.cu", "softmax.cu", "nms.cu",
-           "peer_exchange.cu"]
+           "peer_exchange.cu", "sample.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wextra", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 

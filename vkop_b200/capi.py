@@ -28,6 +28,7 @@ EXPORTS = [
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
     "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
     "vkop_cuda_packets_push", "vkop_cuda_packets_wait", "vkop_cuda_yolo_nms",
+    "vkop_cuda_sample_topk",
 ]
 
 
@@ -82,6 +83,7 @@ def lib() -> C.CDLL:
         L.vkop_cuda_packets_push.argtypes = [vp, sz, vp, vp, C.c_int32, C.c_int32, C.c_uint32, vp, vp]
         L.vkop_cuda_packets_wait.argtypes = [vp, C.c_int32, C.c_uint32, C.c_uint32, vp, vp]
         L.vkop_cuda_yolo_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, sz, vp]
+        L.vkop_cuda_sample_topk.argtypes = [vp, C.c_int32, vp, C.c_int32, C.c_int64, C.c_int32, C.c_float, vp, vp, vp, vp]
         L.vkop_cuda_static_scratch_bytes.restype = sz
         L.vkop_cuda_softmax_topk_static.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp]
         _lib = L
@@ -195,6 +197,21 @@ def yolo_nms(head: torch.Tensor, center_point_box: int = 1, max_output_boxes_per
     check(lib().vkop_cuda_yolo_nms(C.byref(desc), head.data_ptr(), rows.data_ptr(), count.data_ptr(), workspace.ptr,
                                    workspace.buf.numel(), _stream()), "yolo_nms")
     return rows, count
+
+
+def sample_topk(values: torch.Tensor, indices: torch.Tensor, top_p: float, u: torch.Tensor):
+    """Sampling tail over the survivors of softmax_topk.  Returns (choice int32 [rows], token [rows])."""
+    if not (values.is_cuda and indices.is_cuda and u.is_cuda):
+        raise RuntimeError("vkop_b200 runs on CUDA device memory only")
+    rows, k = values.shape
+    assert indices.shape == values.shape and u.shape == (rows,) and u.dtype == torch.float32
+    values, indices, u = values.contiguous(), indices.contiguous(), u.contiguous()
+    choice = torch.empty(rows, dtype=torch.int32, device=values.device)
+    token = torch.empty(rows, dtype=indices.dtype, device=values.device)
+    check(lib().vkop_cuda_sample_topk(values.data_ptr(), dtype_tag(values), indices.data_ptr(),
+                                      I64 if indices.dtype == torch.int64 else I32, rows, k, float(top_p), u.data_ptr(),
+                                      choice.data_ptr(), token.data_ptr(), _stream()), "sample_topk")
+    return choice, token
 
 
 def packets_push(packets: torch.Tensor, peer_slots: torch.Tensor, peer_flags: torch.Tensor, rank: int, world: int,

@@ -256,6 +256,16 @@ int vkop_cuda_yolo_nms(const vkop_nms_desc *desc, const void *head, int32_t *out
     return launch_nms(*desc, h, h + 4 * n, out_rows, out_count, workspace, static_cast<cudaStream_t>(stream), plane, plane, n);
 }
 
+int vkop_cuda_sample_topk(const void *values, int32_t dtype, const void *indices, int32_t index_dtype, int64_t rows,
+                          int32_t k, float top_p, const float *u, int32_t *out_choice, void *out_token, void *stream) {
+    if (rows < 0 || k < 1 || k > 4096 || !(top_p > 0.0f) || (index_dtype != VKOP_I32 && index_dtype != VKOP_I64))
+        return VKOP_INVALID_ARG;
+    if (rows > 0 && (!values || !indices || !u || !out_choice || !out_token))
+        return VKOP_INVALID_ARG;
+    return launch_sample_topk(values, dtype, indices, index_dtype, rows, k, top_p, u, out_choice, out_token,
+                              static_cast<cudaStream_t>(stream));
+}
+
 int vkop_cuda_packets_push(const void *packets, size_t packets_bytes, void *const *peer_slots, void *const *peer_flags,
                            int32_t rank, int32_t world, uint32_t seq, void *tickets, void *stream) {
     if (!packets || !peer_slots || !peer_flags || !tickets || world < 1 || world > 1024 || rank < 0 || rank >= world ||

@@ -66,6 +66,10 @@ int launch_nms(const vkop_nms_desc &d, const void *boxes, const void *scores, in
                void *workspace, cudaStream_t stream, int64_t score_bstride = 0, int64_t box_bstride = 0,
                int64_t box_cstride = 0);
 
+// ---- sampling tail (sample.cu) ----
+int launch_sample_topk(const void *values, int dtype, const void *indices, int index_dtype, int64_t rows, int k, float top_p,
+                       const float *u, int32_t *out_choice, void *out_token, cudaStream_t stream);
+
 // ---- packet exchange over peer memory (peer_exchange.cu) ----
 int launch_packets_push(const void *packets, size_t bytes, void *const *peer_slots, void *const *peer_flags, int rank,
                         int world, uint32_t seq, void *tickets, cudaStream_t stream);
