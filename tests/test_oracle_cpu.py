@@ -7,6 +7,7 @@ import os
 import re
 
 import numpy as np
+import pytest
 import torch
 
 import oracle
@@ -217,6 +218,21 @@ def test_planner_serves_every_shape_and_flag_without_a_device():
                             if path == capi.PATH_AUTO:
                                 assert rc == capi.OK, ("the automatic choice must serve", rows, cols, dtype, k, flags)
     assert served > 5000
+
+
+def test_oracle_sampling_known_answers():
+    v = np.array([[0.5, 0.3, 0.1, 0.05]], np.float32)
+    ids = np.array([[7, 3, 9, 1]])
+    pick = lambda top_p, u: tuple(int(a[0]) for a in oracle.sample_topk(v, ids, top_p, np.array([u], np.float32)))
+    # all four kept (sum 0.95): prefix sums 0.5 / 0.8 / 0.9 / 0.95 against u * 0.95
+    assert pick(1.0, 0.0) == (0, 7) and pick(1.0, 0.51) == (0, 7)
+    assert pick(1.0, 0.85) == (2, 9) and pick(1.0, 0.99) == (3, 1)
+    # top_p 0.8: 0.76 is reached by the first two; draws stay inside them
+    assert pick(0.8, 0.85) == (1, 3) and pick(0.8, 0.99) == (1, 3) and pick(0.8, 0.1) == (0, 7)
+    # a tiny nucleus is the best candidate alone
+    assert pick(0.01, 0.999) == (0, 7)
+    with pytest.raises(ValueError):
+        oracle.sample_topk(v, ids, 0.0, np.array([0.5], np.float32))
 
 
 def test_product_has_no_cpu_path():
