@@ -178,6 +178,27 @@ static void test_nms(Env &env) {
             EXPECT((*out)[i] == want[i], "Nms row value %lld", static_cast<long long>(i));
         if (total * 3 < out->num_elements())
             EXPECT((*out)[total * 3] == -1, "Nms: the row after the result must be (-1,-1,-1)");
+        // the same problem as one detection head [B, 4 + C, N]: coordinate planes, then the score planes
+        auto head = std::make_shared<Tensor<float>>(std::vector<int>{B, 4 + C, N});
+        for (int b = 0; b < B; b++) {
+            for (int q = 0; q < 4; q++)
+                for (int i = 0; i < N; i++)
+                    (*head)[(static_cast<int64_t>(b) * (4 + C) + q) * N + i] = (*boxes)[(static_cast<int64_t>(b) * N + i) * 4 + q];
+            for (int c = 0; c < C; c++)
+                for (int i = 0; i < N; i++)
+                    (*head)[(static_cast<int64_t>(b) * (4 + C) + 4 + c) * N + i] = (*scores)[(static_cast<int64_t>(b) * C + c) * N + i];
+        }
+        auto out2 = std::make_shared<Tensor<int>>(true);
+        std::unique_ptr<ops::Operator> op2;
+        run_op(env, "Nms", {head}, {out2},
+               {{"max_output_boxes_per_class", std::to_string(max_per_class)},
+                {"iou_threshold", std::to_string(iou_thr)},
+                {"score_threshold", std::to_string(score_thr)}},
+               &op2);
+        EXPECT(dynamic_cast<ops::Nms *>(op2.get())->last_count() == total, "Nms on a head: count");
+        out2->copyToCPU(env.cmdpool);
+        for (int64_t i = 0; i < total * 3 && i < out2->num_elements(); i++)
+            EXPECT((*out2)[i] == want[i], "Nms on a head: row value %lld", static_cast<long long>(i));
     }
 }
 

@@ -2,7 +2,8 @@
 // Attributes "center_point_box" (0), "iou_threshold" (0), "score_threshold"
 // (0), "max_output_boxes_per_class" (0 = unlimited), as the reference, plus
 // "pre_topk" (0): only the best pre_topk candidates of a class enter the sweep.
-// Inputs: boxes [B, N, 4] and scores [B, C, N], fp32.  Output: int rows
+// Inputs: boxes [B, N, 4] and scores [B, C, N], fp32 -- or one detection head
+// [B, 4 + C, N] (coordinate planes, then score planes), used in place.  Output: int rows
 // (batch, class, box).  Differences from the reference (its shader writes rows
 // at atomically claimed offsets, sizes the output without the batch factor and
 // never clears its counter, ops/Nms.hpp:79-86,105-106): rows come in
@@ -47,17 +48,34 @@ class Nms : public Operator {
   private:
     void execute(const std::vector<std::shared_ptr<core::ITensor>> &inputs,
                  const std::vector<std::shared_ptr<core::ITensor>> &outputs) override {
-        const auto box_shape = inputs[0]->getShape();
-        const auto score_shape = inputs[1]->getShape();
-        if (box_shape.size() != 3 || score_shape.size() != 3 || box_shape[2] != 4)
-            throw std::invalid_argument("Nms: boxes must be [B, N, 4] and scores [B, C, N]");  // the reference asserts
-        if (inputs[0]->dtype() != typeid(float) || inputs[1]->dtype() != typeid(float))
-            throw std::invalid_argument("Nms: boxes and scores must be float tensors");
+        // One input: a detection head [B, 4 + C, N] (coordinate planes, then class-score planes), used in
+        // place.  Two inputs: boxes [B, N, 4] and scores [B, C, N] as in the reference.
+        const bool head = inputs.size() == 1;
+        int batch, num_boxes, num_class;
+        if (head) {
+            const auto shape = inputs[0]->getShape();
+            if (shape.size() != 3 || shape[1] <= 4)
+                throw std::invalid_argument("Nms: a single input must be a detection head [B, 4 + C, N]");
+            if (inputs[0]->dtype() != typeid(float))
+                throw std::invalid_argument("Nms: the detection head must be a float tensor");
+            batch = shape[0];
+            num_class = shape[1] - 4;
+            num_boxes = shape[2];
+        } else {
+            const auto box_shape = inputs[0]->getShape();
+            const auto score_shape = inputs[1]->getShape();
+            if (box_shape.size() != 3 || score_shape.size() != 3 || box_shape[2] != 4)
+                throw std::invalid_argument("Nms: boxes must be [B, N, 4] and scores [B, C, N]");  // the reference asserts
+            if (inputs[0]->dtype() != typeid(float) || inputs[1]->dtype() != typeid(float))
+                throw std::invalid_argument("Nms: boxes and scores must be float tensors");
+            batch = box_shape[0];
+            num_boxes = box_shape[1];
+            num_class = score_shape[1];
+            if (score_shape[0] != batch || score_shape[2] != num_boxes)
+                throw std::invalid_argument("Nms: boxes and scores disagree on batch or box count");
+        }
         if (outputs[0]->dtype() != typeid(int))
             throw std::invalid_argument("Nms: the output must be an int tensor");
-        const int batch = box_shape[0], num_boxes = box_shape[1], num_class = score_shape[1];
-        if (score_shape[0] != batch || score_shape[2] != num_boxes)
-            throw std::invalid_argument("Nms: boxes and scores disagree on batch or box count");
         int per_class = num_boxes;
         if (pre_topk_ > 0 && pre_topk_ < per_class)
             per_class = pre_topk_;
@@ -82,9 +100,14 @@ class Nms : public Operator {
         void *out = device_of(outputs[0]);
         cuda_check(cudaMemsetAsync(out, 0xFF, static_cast<size_t>(outputs[0]->num_elements()) * sizeof(int), stream()),
                    "cudaMemsetAsync");  // rows past the result read (-1, -1, -1)
-        check(vkop_cuda_nms(&d, device_of(inputs[0]), device_of(inputs[1]), static_cast<int32_t *>(out),
-                            static_cast<int32_t *>(count_->ptr()), ws, workspace_bytes(), stream()),
-              "vkop_cuda_nms");
+        if (head)
+            check(vkop_cuda_yolo_nms(&d, device_of(inputs[0]), static_cast<int32_t *>(out), static_cast<int32_t *>(count_->ptr()),
+                                     ws, workspace_bytes(), stream()),
+                  "vkop_cuda_yolo_nms");
+        else
+            check(vkop_cuda_nms(&d, device_of(inputs[0]), device_of(inputs[1]), static_cast<int32_t *>(out),
+                                static_cast<int32_t *>(count_->ptr()), ws, workspace_bytes(), stream()),
+                  "vkop_cuda_nms");
     }
 
     int center_point_box_ = 0, max_output_boxes_per_class_ = 0, pre_topk_ = 0;
