@@ -54,6 +54,10 @@ struct Elem<float> {
         f[2] = __uint_as_float(v.z);
         f[3] = __uint_as_float(v.w);
     }
+    // largest element of the vector (NaN elements are passed over, as fmaxf does)
+    __device__ static __forceinline__ float vector_max(const uint4 &v) {
+        return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
+    }
     __device__ static __forceinline__ float from_storage(float v) { return v; }
     __device__ static __forceinline__ float to_storage(float v) { return v; }
 };
@@ -72,6 +76,13 @@ struct Elem<__half> {
             f[2 * i + 1] = p.y;
         }
     }
+    // packed maxima: three instructions for eight elements, then the two halves of the last word
+    __device__ static __forceinline__ float vector_max(const uint4 &v) {
+        const __half2 a = *reinterpret_cast<const __half2 *>(&v.x), b = *reinterpret_cast<const __half2 *>(&v.y);
+        const __half2 c = *reinterpret_cast<const __half2 *>(&v.z), e = *reinterpret_cast<const __half2 *>(&v.w);
+        const float2 f = __half22float2(__hmax2(__hmax2(a, b), __hmax2(c, e)));
+        return fmaxf(f.x, f.y);
+    }
     __device__ static __forceinline__ float from_storage(__half v) { return __half2float(v); }
     __device__ static __forceinline__ __half to_storage(float v) { return __float2half_rn(v); }
 };
@@ -87,6 +98,12 @@ struct Elem<__nv_bfloat16> {
             f[2 * i] = __uint_as_float(w[i] << 16);
             f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
         }
+    }
+    __device__ static __forceinline__ float vector_max(const uint4 &v) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&v.x), b = *reinterpret_cast<const __nv_bfloat162 *>(&v.y);
+        const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162 *>(&v.z), e = *reinterpret_cast<const __nv_bfloat162 *>(&v.w);
+        const float2 f = __bfloat1622float2(__hmax2(__hmax2(a, b), __hmax2(c, e)));
+        return fmaxf(f.x, f.y);
     }
     __device__ static __forceinline__ float from_storage(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 to_storage(float v) { return __float2bfloat16_rn(v); }

@@ -714,12 +714,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         float vm = -INFINITY;
 #pragma unroll
         for (int j = 0; j < VECS; j++) {
-            float f[EPV];
-            Elem<T>::unpack(d[j], f);
-            float a = f[0];
-#pragma unroll
-            for (int e = 1; e < EPV; e++)
-                a = fmaxf(a, f[e]);
+            const float a = Elem<T>::vector_max(d[j]);
             vmax[j] = a;
             vm = fmaxf(vm, a);
         }
