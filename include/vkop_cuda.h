@@ -53,7 +53,9 @@ typedef enum vkop_select_path {
     VKOP_PATH_AUTO = 0,
     VKOP_PATH_CHUNK = 1,  /* one CTA per chunk of a row, the chunk held in registers */
     VKOP_PATH_RADIX = 2,  /* multi-pass radix select (large k, very long rows) */
-    VKOP_PATH_STREAM = 3  /* persistent CTAs streaming tiles with a running threshold */
+    VKOP_PATH_STREAM = 3, /* persistent CTAs streaming cp.async tiles with a running threshold (any alignment) */
+    VKOP_PATH_BULK = 4    /* persistent CTAs fed by bulk copies into a shared-memory ring: long rows that start on
+                             16-byte boundaries; AUTO prefers it where it applies */
 } vkop_select_path;
 
 /* The logits are complete and visible before the call is enqueued: no earlier

@@ -205,6 +205,26 @@ def ref_nms_problem(boxes_n4: np.ndarray, scores_n: np.ndarray, center_point_box
     return kept[:n].copy()
 
 
+def ref_unfused_softmax_topk(logits: np.ndarray, k: int, inv_temperature: float = 1.0, dtype: int | None = None):
+    """Emulation of the reference's UNFUSED order (ops/Softmax.hpp:61-141 followed by ops/Topk.hpp:95-217 on the
+    softmax output): the probabilities are rounded to the pipeline's storage type first (fp32, or fp16 / bf16 bits),
+    and TopK then selects on those rounded probabilities (value descending, lower index first among equal values),
+    whereas the fused operator selects on the stored logits.  Distinct logits can round to equal probabilities, so
+    the two orders may differ; this function is there to list where.  Returns (rounded probabilities f32 [rows,k],
+    indices i64 [rows,k])."""
+    dt = dtype_of(logits, dtype)
+    x = _as_storage(logits, dt)
+    p = softmax(x, -1, inv_temperature, dtype=dt, sum_mode=SUM_F32_SEQUENTIAL)
+    if dt == F16:
+        p = p.astype(np.float16).astype(np.float32)
+    elif dt == BF16:
+        b = p.view(np.uint32)
+        b = (b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)  # round to nearest even
+        p = b.view(np.float32)
+    order = np.argsort(-p, axis=1, kind="stable")[:, :k]
+    return np.take_along_axis(p, order, axis=1), order.astype(np.int64)
+
+
 def order_key(x: float) -> int:
     return int(lib().oracle_order_key(C.c_float(x)))
 

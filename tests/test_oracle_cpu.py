@@ -246,3 +246,30 @@ def test_product_has_no_cpu_path():
         raise AssertionError("a CPU tensor must be rejected")
     src = open(os.path.join(ROOT, "vkop_b200", "capi.py")).read() + open(os.path.join(ROOT, "vkop_b200", "sharded.py")).read()
     assert "import oracle" not in src and "from oracle" not in src
+
+
+def test_unfused_order_emulation_against_the_contract():
+    """The reference runs Softmax, rounds the probabilities to the pipeline's type, then TopK on those; the fused
+    operator selects on the stored logits.  On every benchmark configuration the two orders give the same indices
+    (the rows where they differ are counted and must be none); a crafted fp16 row whose two runner-up
+    probabilities round to the same subnormal shows what a difference looks like."""
+    cases = [("C1", workloads.classifier_head(), 5, 1.0), ("C2", workloads.batched_classifier(), 5, 1.0),
+             ("C3 f32", workloads.llm_vocab(rows=16), 50, 1.25),
+             ("C3 f16", workloads.llm_vocab(dtype=torch.float16), 50, 1.25),
+             ("C5 bf16", workloads.sharded_vocab(rows=8), 64, 1.0)]
+    for name, x, k, inv_t in cases:
+        xa, dt = util.to_oracle_array(x), util.ORACLE_DTYPE[x.dtype]
+        _, i = oracle.softmax_topk(xa, k, inv_t, dtype=dt)
+        _, pi = oracle.ref_unfused_softmax_topk(xa, k, inv_t, dtype=dt)
+        differing = int((i != pi).any(axis=1).sum())
+        assert differing == 0, f"{name}: {differing} rows where the unfused order differs"
+    x = torch.full((1, 64), -30.0, dtype=torch.float16)
+    x[0, 0] = 10.0
+    x[0, 5] = -5.004   # fp16 neighbours: distinct logits ...
+    x[0, 9] = -5.0     # ... whose probabilities (3e-7) round to one fp16 subnormal
+    xa = util.to_oracle_array(x)
+    assert xa[0, 5] != xa[0, 9]
+    _, i = oracle.softmax_topk(xa, 3, dtype=oracle.F16)
+    pv, pi = oracle.ref_unfused_softmax_topk(xa, 3, dtype=oracle.F16)
+    assert list(i[0]) == [0, 9, 5]            # the contract: larger logit first
+    assert pv[0, 1] == pv[0, 2] and list(pi[0]) == [0, 5, 9]   # the unfused order: equal probabilities, lower index first

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(HERE, "libvkop_cuda.so")
 F32, F16, BF16 = 0, 1, 2
 I32, I64 = 0, 1
 VALUE_PROBABILITY, VALUE_RAW = 0, 1
-PATH_AUTO, PATH_CHUNK, PATH_RADIX, PATH_STREAM = 0, 1, 2, 3
+PATH_AUTO, PATH_CHUNK, PATH_RADIX, PATH_STREAM, PATH_BULK = 0, 1, 2, 3, 4
 FLAG_INPUT_READY = 1
 OK, INVALID_ARG, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, TIMEOUT = 0, -1, -2, -3, -4, -5
 

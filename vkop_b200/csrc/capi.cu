@@ -27,7 +27,7 @@ static int validate_select(const vkop_softmax_topk_desc *d, bool check_ptrs, con
         return VKOP_INVALID_ARG;
     if (d->row_stride != 0 && d->row_stride < d->cols)
         return VKOP_INVALID_ARG;
-    if (d->path < VKOP_PATH_AUTO || d->path > VKOP_PATH_STREAM || d->splits < 0)
+    if (d->path < VKOP_PATH_AUTO || d->path > VKOP_PATH_BULK || d->splits < 0)
         return VKOP_INVALID_ARG;
     if (d->index_offset < 0 || d->index_offset + d->cols > 0xFFFFFFFFll)
         return VKOP_INVALID_ARG;
@@ -50,21 +50,32 @@ static int plan_select(const vkop_softmax_topk_desc &d, const void *in, SelectPl
     const int64_t row_bytes = d.cols * (d.dtype == VKOP_F32 ? 4 : 2);
     // rows longer than one CTA's register tile, and enough of them: the streaming kernel
     const bool prefer_stream = row_bytes > 64 * 1024 && d.rows * row_bytes >= (2ll << 20);
-    if (d.path == VKOP_PATH_STREAM || (d.path == VKOP_PATH_AUTO && prefer_stream && d.splits == 0)) {
+    if (d.path == VKOP_PATH_STREAM || d.path == VKOP_PATH_BULK || (d.path == VKOP_PATH_AUTO && prefer_stream && d.splits == 0)) {
+        // Two kernels serve this kind: the bulk-copy kernel for 16-byte aligned long rows, the cp.async
+        // kernel for everything else.  Both number their calls in one shared head of the workspace, and
+        // each has its own part behind it, so calls with aligned and unaligned pointers may alternate.
         const bool base_aligned = reinterpret_cast<uintptr_t>(in) % 16 == 0;
-        rc = plan_stream(d, base_aligned, &plan->stream);
+        const bool want_bulk = d.path != VKOP_PATH_STREAM, want_stream = d.path != VKOP_PATH_BULK;
+        const int rcb = want_bulk ? plan_bulk(d, in ? base_aligned : true, &plan->bulk) : VKOP_UNSUPPORTED;
+        size_t stream_bytes = 0;
+        rc = want_stream ? plan_stream(d, base_aligned, &plan->stream) : VKOP_UNSUPPORTED;
         if (rc == VKOP_OK) {
+            stream_bytes = plan->stream.counters_bytes + plan->stream.lists_bytes;
+            StreamPlan other;
+            if (plan_stream(d, !base_aligned, &other) == VKOP_OK && other.counters_bytes + other.lists_bytes > stream_bytes)
+                stream_bytes = other.counters_bytes + other.lists_bytes;
+        }
+        if (rc == VKOP_OK || rcb == VKOP_OK) {
             plan->kind = kSelectStream;
-            plan->bytes = plan->stream.counters_bytes + plan->stream.lists_bytes;
-            if (!in) {
-                StreamPlan other;
-                if (plan_stream(d, false, &other) == VKOP_OK && other.counters_bytes + other.lists_bytes > plan->bytes)
-                    plan->bytes = other.counters_bytes + other.lists_bytes;
-            }
+            plan->use_bulk = rcb == VKOP_OK;
+            const size_t bulk_bytes = rcb == VKOP_OK ? plan->bulk.counters_bytes + plan->bulk.lists_bytes : 0;
+            plan->bulk_off = stream_common_bytes(d.rows);
+            plan->stream_off = plan->bulk_off + bulk_bytes;
+            plan->bytes = plan->stream_off + stream_bytes;
             return VKOP_OK;
         }
-        if (d.path == VKOP_PATH_STREAM)
-            return rc;
+        if (d.path == VKOP_PATH_STREAM || d.path == VKOP_PATH_BULK)
+            return d.path == VKOP_PATH_BULK ? rcb : rc;
     }
     if (d.path != VKOP_PATH_RADIX)
         rc = plan_chunk(d, &plan->chunk);
@@ -94,7 +105,10 @@ static int run_select(const vkop_softmax_topk_desc &d, const void *in, void *ov,
         return VKOP_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (plan.kind) {
-    case kSelectStream: return launch_stream(d, plan.stream, in, ov, oi, packets_out, ws, need_sum, s);
+    case kSelectStream:
+        if (plan.use_bulk)
+            return launch_bulk(d, plan.bulk, in, ov, oi, packets_out, ws, static_cast<char *>(ws) + plan.bulk_off, need_sum, s);
+        return launch_stream(d, plan.stream, in, ov, oi, packets_out, ws, static_cast<char *>(ws) + plan.stream_off, need_sum, s);
     case kSelectRadix: return launch_radix(d, plan.radix, in, ov, oi, packets_out, ws, need_sum, s);
     default: return launch_chunk(d, plan.chunk, in, ov, oi, packets_out, ws, need_sum, s);
     }

@@ -19,6 +19,15 @@ void note_launch(int n = 1);
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? VKOP_OK : VKOP_CUDA_ERROR; }
 
+// Barrier over the whole CTA (BAR == 0) or over the N threads that share named barrier BAR.
+template <int BAR, int N>
+__device__ __forceinline__ void cta_sync() {
+    if constexpr (BAR == 0)
+        __syncthreads();
+    else
+        asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(N) : "memory");
+}
+
 // float -> uint32 such that a > b <=> key(a) > key(b); -0 maps with +0, every
 // NaN maps to the largest key.  No valid value maps to key 0.
 __device__ __forceinline__ uint32_t order_key(float x) {
@@ -58,6 +67,10 @@ struct Elem<float> {
     __device__ static __forceinline__ float vector_max(const uint4 &v) {
         return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
     }
+    __device__ static __forceinline__ bool vector_has_nan(const uint4 &v) {
+        const float a = __uint_as_float(v.x), b = __uint_as_float(v.y), c = __uint_as_float(v.z), e = __uint_as_float(v.w);
+        return (a != a) | (b != b) | (c != c) | (e != e);
+    }
     __device__ static __forceinline__ float from_storage(float v) { return v; }
     __device__ static __forceinline__ float to_storage(float v) { return v; }
 };
@@ -83,6 +96,11 @@ struct Elem<__half> {
         const float2 f = __half22float2(__hmax2(__hmax2(a, b), __hmax2(c, e)));
         return fmaxf(f.x, f.y);
     }
+    // a half is NaN when its magnitude bits exceed 0x7C00: adding 0x03FF then carries into bit 15
+    __device__ static __forceinline__ bool vector_has_nan(const uint4 &v) {
+        const uint32_t m = 0x7FFF7FFFu, a = 0x03FF03FFu;
+        return ((((v.x & m) + a) | ((v.y & m) + a) | ((v.z & m) + a) | ((v.w & m) + a)) & 0x80008000u) != 0u;
+    }
     __device__ static __forceinline__ float from_storage(__half v) { return __half2float(v); }
     __device__ static __forceinline__ __half to_storage(float v) { return __float2half_rn(v); }
 };
@@ -104,6 +122,11 @@ struct Elem<__nv_bfloat16> {
         const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162 *>(&v.z), e = *reinterpret_cast<const __nv_bfloat162 *>(&v.w);
         const float2 f = __bfloat1622float2(__hmax2(__hmax2(a, b), __hmax2(c, e)));
         return fmaxf(f.x, f.y);
+    }
+    // a bfloat16 is NaN when its magnitude bits exceed 0x7F80: adding 0x007F then carries into bit 15
+    __device__ static __forceinline__ bool vector_has_nan(const uint4 &v) {
+        const uint32_t m = 0x7FFF7FFFu, a = 0x007F007Fu;
+        return ((((v.x & m) + a) | ((v.y & m) + a) | ((v.z & m) + a) | ((v.w & m) + a)) & 0x80008000u) != 0u;
     }
     __device__ static __forceinline__ float from_storage(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 to_storage(float v) { return __float2bfloat16_rn(v); }

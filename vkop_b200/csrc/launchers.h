@@ -34,8 +34,23 @@ struct StreamPlan {
 };
 // base_aligned: the logits pointer is a multiple of 16 (rows then are too when the row stride is)
 int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *plan);
+// common_ws: the shared head of the workspace (stream_common_bytes); workspace: this kernel's own part
 int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const void *logits, void *out_values,
-                  void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream);
+                  void *out_indices, void *packets_out, void *common_ws, void *workspace, int need_sum, cudaStream_t stream);
+
+// ---- bulk-copy streaming path (softmax_topk_bulk.cu): long, 16-byte aligned rows ----
+struct BulkPlan {
+    int grid;
+    int64_t per_cta, nvv, vstride;
+    int maxparts, list_cap;
+    size_t counters_bytes, lists_bytes, smem_bytes;
+};
+// Head of a workspace of the streaming kernels, shared by both: call counter, arrival counter and
+// status word (256 bytes), then one counter of finished calls per row.
+size_t stream_common_bytes(int64_t rows);
+int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan);
+int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const void *logits, void *out_values, void *out_indices,
+                void *packets_out, void *common_ws, void *bulk_ws, int need_sum, cudaStream_t stream);
 
 // ---- radix path (radix_select.cu) ----
 struct RadixPlan {
@@ -51,6 +66,9 @@ struct SelectPlan {
     int kind;
     ChunkPlan chunk;
     StreamPlan stream;
+    BulkPlan bulk;
+    int use_bulk;             // streaming kind: this call runs the bulk-copy kernel
+    size_t bulk_off, stream_off;  // streaming kind: where the two kernels' own parts of the workspace start
     RadixPlan radix;
     size_t bytes;
 };

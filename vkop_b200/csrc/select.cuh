@@ -34,27 +34,11 @@ struct ChunkParams {
     int64_t vstride;   // vectors between the starts of consecutive rows (rows 16-byte aligned only)
     int parts_per_row; // > 0: every row is cut into this many CTAs and no CTA crosses a row
     int input_ready;   // the logits were complete before this launch was enqueued
-    unsigned long long *arrivals;  // CTAs that ever started on this workspace (gives every call its number)
-#ifdef VKOP_PHASE_PROF
-    int prof_seq;      // development aid: sequence number of the call
-#endif
+    // calls on one workspace number themselves (streaming kernels): the call counter, the CTAs of the
+    // current call that have drawn their arrival ticket, and per row the calls whose result is written
+    unsigned int *epoch_word, *arrive_word, *row_done;
 };
 
-#ifdef VKOP_PHASE_PROF
-// Development aid, compiled only on request: per-CTA timestamps of the kernels' phases, for the last
-// eight launches (slot = launch sequence number modulo 8).
-static __device__ unsigned long long g_phase_prof[8 * 1024 * 16];
-__device__ __forceinline__ void prof_mark(int seq, int slot) {
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_phase_prof[((seq & 7) * 1024 + blockIdx.x) * 16 + slot] = t;
-    }
-}
-#define PROF_MARK(s) prof_mark(p.prof_seq, s)
-#else
-#define PROF_MARK(s)
-#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -104,9 +88,10 @@ __device__ __forceinline__ uint64_t warp_sort_desc(uint64_t v, int lane) {
 
 // Exact selection of the best min(k, n) of n distinct candidates held in shared
 // memory (list[0..n)); `work` is a second region of at least n slots.  The
-// survivors are emitted at their rank.  Executed by the whole CTA; list and
-// work are clobbered.
-template <typename T, int THREADS>
+// survivors are emitted at their rank.  Executed by THREADS threads (the whole
+// CTA, or with BAR > 0 the threads 0 .. THREADS-1 that share named barrier
+// BAR); list and work are clobbered.
+template <typename T, int THREADS, int BAR = 0>
 __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, uint64_t *list, int n, uint64_t *work, float M,
                                 float S, unsigned long long *list_out, int *s_tmp) {
     constexpr int NW = THREADS / 32;
@@ -145,7 +130,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
             s_tmp[0] = 0x7FFFFFFF;  // threshold key >> 1 (kept positive for atomicMin on int)
             s_tmp[1] = 0;
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         for (int g = warp; g < nfull; g += NW) {
             uint32_t cur = cand_key(src[g * 32 + lane]);
             uint32_t rth = 0;
@@ -158,7 +143,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
             if (lane == 0)
                 atomicMin(&s_tmp[0], static_cast<int>(rth >> 1));
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         const uint32_t tkey = static_cast<uint32_t>(s_tmp[0]) << 1;  // rounded down: keeps the bound valid
         for (int i = tid; i < n2; i += THREADS) {
             const uint64_t c = src[i];
@@ -167,19 +152,18 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
                 work[pos] = c;
             }
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         const int n3 = s_tmp[1];
         uint64_t *t = src;
         src = work;
         work = t;
         const bool progress = n3 * 4 <= n2 * 3;
         n2 = n3;
-        __syncthreads();  // s_tmp is reused by the next round
+        cta_sync<BAR, THREADS>();  // s_tmp is reused by the next round
         if (!progress)
             break;
     }
     // ---- sort groups of 32, then rank every survivor against the other groups ----
-    PROF_MARK(10);
     const int ng = (n2 + 31) / 32;
     for (int g = warp; g < ng; g += NW) {
         const int i = g * 32 + lane;
@@ -187,8 +171,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
         v = warp_sort_desc(v, lane);
         work[i] = v;
     }
-    __syncthreads();
-    PROF_MARK(11);
+    cta_sync<BAR, THREADS>();
     for (int g = warp; g < ng; g += NW) {
         const uint64_t me = work[g * 32 + lane];
         int rank = lane;
@@ -219,7 +202,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
 // Exact selection of the kk best (key, ~index) values of a chunk by an 8-bit
 // most-significant-digit radix select over the 64-bit candidate value.  The
 // chunk is re-read from memory.  Leaves exactly kk candidates in s_cand.
-template <typename T, int THREADS>
+template <typename T, int THREADS, int BAR = 0>
 __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int64_t v1, int head, int64_t cols,
                                              int negate, int kk, uint64_t *s_cand, int *s_count, int *s_hist,
                                              int *s_pick) {
@@ -231,7 +214,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
         const int shift = pass * 8;
         for (int i = tid; i < 256; i += THREADS)
             s_hist[i] = 0;
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         for (int64_t v = v0 + tid; v < v1; v += THREADS) {
             uint4 d = vbase[v];
             if (negate) {
@@ -250,7 +233,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
                 }
             }
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         if (tid == 0) {
             int cum = 0, d = 255;
             for (; d > 0; --d) {
@@ -263,7 +246,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
             s_pick[1] = need - cum;
             s_pick[2] = s_hist[d];
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         prefix |= static_cast<uint64_t>(s_pick[0]) << shift;
         mask |= 0xFFull << shift;
         need = s_pick[1];
@@ -272,7 +255,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
     }
     if (tid == 0)
         *s_count = 0;
-    __syncthreads();
+    cta_sync<BAR, THREADS>();
     for (int64_t v = v0 + tid; v < v1; v += THREADS) {
         uint4 d = vbase[v];
         if (negate) {
@@ -294,7 +277,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
             }
         }
     }
-    __syncthreads();
+    cta_sync<BAR, THREADS>();
 }
 
 // Gathers the candidate lists of the G parts of one row into shared memory,
@@ -308,7 +291,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
 // PEERS: the lists are not in global memory: list g sits at `lists` in the
 // shared memory of CTA g of this thread-block cluster (at most 32 lists of at
 // most 512 candidates).
-template <typename T, int THREADS, bool PEERS = false>
+template <typename T, int THREADS, bool PEERS = false, int BAR = 0>
 __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, const unsigned long long *lists, int64_t stride, int G,
                             uint64_t *s_buf, uint64_t *s_sel, float *s_red, int *s_int, int *s_tmp) {
     constexpr int NW = THREADS / 32;
@@ -354,8 +337,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
         }
         if (tid == 0)
             s_tmp[0] = 0;
-        __syncthreads();
-        PROF_MARK(8);
+        cta_sync<BAR, THREADS>();
         uint32_t trow = 0;
         M = -INFINITY;
         for (int q = 0; q < G; q++) {
@@ -385,10 +367,9 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
                 }
             }
         }
-        __syncthreads();
+        cta_sync<BAR, THREADS>();
         n = s_tmp[0];
-        __syncthreads();  // s_tmp is reused by the selection
-        PROF_MARK(9);
+        cta_sync<BAR, THREADS>();  // s_tmp is reused by the selection
     } else {
         // statistics and list offsets (one warp walks the headers)
         if (warp == 0) {
@@ -427,8 +408,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
                 s_int[0] = base;
             }
         }
-        __syncthreads();
-        PROF_MARK(8);
+        cta_sync<BAR, THREADS>();
         M = s_red[0];
         S = s_red[1];
         n = s_int[0];
@@ -440,8 +420,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
             for (int i = lane; i < end - off; i += 32)
                 s_buf[off + i] = __ldcg(src + i);
         }
-        __syncthreads();
-        PROF_MARK(9);
+        cta_sync<BAR, THREADS>();
     }
     const int nsel = n < p.k ? n : p.k;
     if (p.packets_out && tid == 0) {
@@ -451,7 +430,7 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
         pk[2] = static_cast<uint32_t>(nsel);
         pk[3] = 0;
     }
-    select_and_emit<T, THREADS>(p, row, s_buf, n, s_sel ? s_sel : s_buf + ((n + 31) & ~31), M, S, nullptr, s_tmp);
+    select_and_emit<T, THREADS, BAR>(p, row, s_buf, n, s_sel ? s_sel : s_buf + ((n + 31) & ~31), M, S, nullptr, s_tmp);
 }
 
 }  // namespace vkop_cuda

@@ -58,7 +58,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
 
     if (tid == 0)
         s_count = 0;
-    PROF_MARK(0);
 
     // ---- one pass over memory: the chunk lands in registers ----
     uint4 d[VECS];
@@ -106,7 +105,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
             mt = fmaxf(mt, f[e]);
     }
 
-    PROF_MARK(1);
     // ---- threshold: r-th largest thread maximum per full warp, min over warps ----
     const int nfullw = nvc >= THREADS ? NW : nvc / 32;
     const int r = nfullw > 0 ? (p.k + nfullw - 1) / nfullw : 33;
@@ -152,6 +150,14 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
             for (int e = 0; e < EPV; e++)
                 st += ex2_approx((f[e] - mref) * c1);
         }
+    } else {
+        // no sum to carry a NaN (the maxima pass it over): look for it, and poison the sum that nobody reads
+        bool has_nan = false;
+#pragma unroll
+        for (int j = 0; j < VECS; j++)
+            has_nan |= Elem<T>::vector_has_nan(d[j]);
+        if (has_nan)
+            st = __int_as_float(0x7FC00000);
     }
     if (!allpass) {
         // padding is -inf and T is above -inf: whatever passes is a valid element
@@ -193,7 +199,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
     __syncthreads();
     const float S = warp_sum(lane < NW ? s_red[lane] : 0.0f);
     int C = s_count;
-    PROF_MARK(2);
 
     // valid elements of this chunk, and how many of them the chunk must deliver
     int64_t e0 = v0 * EPV - head, e1 = v1 * EPV - head;
@@ -237,16 +242,13 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
         mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
         mylist[1] = static_cast<unsigned long long>(C);
     }
-    PROF_MARK(3);
     __threadfence();
     __syncthreads();
-    PROF_MARK(4);
     if (tid == 0) {
         const unsigned int t = atomicAdd(&p.counters[row], 1u);
         s_last = (t == static_cast<unsigned int>(p.splits) - 1u);
     }
     __syncthreads();
-    PROF_MARK(5);
     if (!s_last)
         return;
     __threadfence();
@@ -254,7 +256,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
         p.counters[row] = 0;  // ready for the next launch
     merge_lists<T, THREADS>(p, row, p.lists + row * p.splits * lstride, lstride, p.splits, s_cand, nullptr, s_red, s_int, s_tmp);
     __syncthreads();
-    PROF_MARK(6);
 }
 
 // Merge of packets gathered from several GPUs: [shards][rows][packet].

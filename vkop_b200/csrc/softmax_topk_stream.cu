@@ -32,11 +32,12 @@
 // to be done with a row's lists; and results of one row are written in call order.  Both are
 // checked with one acquire load of a per-row counter of finished calls; only when the check fails
 // does the CTA fall back to griddepcontrol.wait for the whole previous call.  Calls number
-// themselves on the device (an arrival ticket per CTA, drawn before the successor is let in), so a
+// themselves on the device (a call counter advanced by the last CTA to arrive, before the successor is let in), so a
 // replayed CUDA graph needs no changing parameter.  Back-to-back calls then overlap several deep.
 #include "common.cuh"
 #include "launchers.h"
 #include "select.cuh"
+#include "stream_ranges.cuh"
 
 namespace vkop_cuda {
 
@@ -45,53 +46,9 @@ constexpr int kStreamThreadsSmall = 256; // calls that overlap: four lighter CTA
 constexpr int kStreamVecs = 4;
 constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
-constexpr int kUnit = 256;            // range boundaries inside a row are multiples of this many vectors
 constexpr int kStreamSlots = 4;       // private candidate slots of one thread
 constexpr int kStreamListCap = 512;   // most candidates one row part publishes
 constexpr int kStreamMaxCluster = 8;  // largest portable thread-block cluster
-
-// Snaps a slot offset inside a row to the nearest allowed boundary.
-__host__ __device__ inline uint32_t snap_in_row(uint32_t v, uint32_t nvv) {
-    const uint32_t units = nvv / kUnit > 0 ? nvv / kUnit : 1;
-    const uint32_t u = (v + kUnit / 2) / kUnit;
-    return u >= units ? nvv : u * kUnit;
-}
-
-// First slot of CTA c (all arithmetic in 32 bits: rows * nvv < 2^32).
-// parts > 0: CTA c serves part c % parts of row c / parts.
-__host__ __device__ inline uint32_t stream_boundary(uint32_t c, uint32_t grid, uint32_t per, uint32_t nvv, uint32_t total,
-                                                    uint32_t parts) {
-    if (c >= grid)
-        return total;
-    if (parts > 0) {
-        const uint32_t r = c / parts, j = c - r * parts;
-        return r * nvv + snap_in_row(static_cast<uint32_t>(static_cast<uint64_t>(j) * nvv / parts), nvv);
-    }
-    const uint64_t v64 = static_cast<uint64_t>(c) * per;
-    if (v64 >= total)
-        return total;
-    const uint32_t V = static_cast<uint32_t>(v64);
-    const uint32_t r = V / nvv;
-    return r * nvv + snap_in_row(V - r * nvv, nvv);
-}
-
-// Largest CTA index whose range starts at or before slot V (V < total).
-__device__ inline uint32_t stream_owner(uint32_t V, uint32_t grid, uint32_t per, uint32_t nvv, uint32_t total, uint32_t parts) {
-    uint32_t c;
-    if (parts > 0) {
-        const uint32_t r = V / nvv;
-        c = r * parts + static_cast<uint32_t>(static_cast<uint64_t>(V - r * nvv) * parts / nvv);
-    } else {
-        c = V / per;
-    }
-    if (c >= grid)
-        c = grid - 1;
-    while (c + 1 < grid && stream_boundary(c + 1, grid, per, nvv, total, parts) <= V)
-        c++;
-    while (c > 0 && stream_boundary(c, grid, per, nvv, total, parts) > V)
-        c--;
-    return c;
-}
 
 // A lower bound of the k-th largest element of the part seen so far, from the running thread
 // maxima (m_t of every thread of the CTA; 0 = no bound).  Any value that at least k thread maxima
@@ -224,7 +181,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     const float c1 = p.inv_t * kLog2e;
     const int64_t lstride = 2 + p.list_cap;
     const int cols = static_cast<int>(p.cols);
-    unsigned int *const row_done = p.counters + 2 * p.rows;  // per row: calls whose result is written
+    unsigned int *const row_done = p.row_done;  // per row: calls whose result is written
     const float m_t = e.m_t, s_t = e.s_t;
     const uint32_t tkey = e.tkey;
     uint64_t *const slot = e.slot;
@@ -236,7 +193,6 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     const bool has_next = e.has_next;
     (void)has_next;
     bool waited = e.waited;
-    PROF_MARK(4);
     // ================= end of a row part: statistics, publish, maybe merge the row =================
     const uint32_t c_first = parts > 0 ? static_cast<uint32_t>(c_row) * parts
                                        : stream_owner(static_cast<uint32_t>(c_row) * nvv, grid, per, nvv, total, parts);
@@ -260,7 +216,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         wkey = max(wkey, __shfl_xor_sync(kFullMask, wkey, o));
     {
         const float mw = key_to_float(wkey);
-        const float sw = warp_sum(m_t == -INFINITY ? 0.0f : s_t * ex2_approx((m_t - mw) * c1));
+        const float sw = warp_sum((m_t == -INFINITY && s_t == s_t) ? 0.0f : s_t * ex2_approx((m_t - mw) * c1));
         if (lane == 0) {
             s_wm0[warp] = wkey;
             s_red[warp] = sw;
@@ -303,7 +259,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     const int held = static_cast<int>((slot - (s_cand + tid)) / THREADS);
     uint32_t tpub = tkey;  // threshold the row merge may rely on
     int C;
-    const bool plain = novf == 0 && !(p.need_sum && S != S);
+    const bool plain = novf == 0 && !(S != S);
     if (plain) {
 #pragma unroll
         for (int q = 0; q < SLOTS; q++) {
@@ -357,7 +313,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
             to_list(s_work[i]);
         __syncthreads();
         C = s_tmp[0];
-        if (C > CAP || novf > CAP || (p.need_sum && S != S)) {
+        if (C > CAP || novf > CAP || S != S) {
             // exact radix select over the part, re-read from L2
             const int fv1 = part_v1 < nvr ? part_v1 : nvr;
             select_fallback<T, THREADS>(vbase, part_v0, fv1, head, p.cols, p.negate, kk, s_cand, sh.count, s_hist, s_pick);
@@ -375,7 +331,6 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         tpub = 0;  // the list holds the part's best, not everything above a threshold
         __syncthreads();
     }
-    PROF_MARK(5);
 
     if (CLUSTER) {
         // ---- the parts of the row meet at the cluster barrier; the first CTA of the row merges
@@ -386,13 +341,10 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         }
         cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
         cluster.sync();
-        PROF_MARK(6);
         if (cluster.block_rank() == 0) {
-            PROF_MARK(7);
             // (the tile stages are free: no CTA of a cluster goes on to another row)
             merge_lists<T, THREADS, true>(p, c_row, mylist, 0, static_cast<int>(parts), s_dyn, s_dyn + 2 * TV, s_red, s_int,
                                           s_tmp);
-            PROF_MARK(12);
         }
         cluster.sync();  // the other CTAs keep their shared memory until it has been read
     } else if (whole) {
@@ -411,7 +363,6 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
                 waited = true;
             }
         }
-        PROF_MARK(7);
         if (p.packets_out && tid == 0) {
             uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
             pk[0] = __float_as_uint(mz);
@@ -425,7 +376,6 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
             const unsigned int d = epoch + 1u;
             asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
         }
-        PROF_MARK(12);
     } else {
     // ---- announce the part; the last part of a row to arrive merges the row ----
         if (tid == 0) {
@@ -452,10 +402,8 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
             s_flag[0] = in_order;
         }
         __syncthreads();
-        PROF_MARK(6);
         const int nparts = s_flag[1];
         if (nparts > 0) {
-            PROF_MARK(7);
             if (!waited && !s_flag[0]) {  // rare: the previous call is still merging this row
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
@@ -470,7 +418,6 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
                 const unsigned int d = epoch + 1u;
                 asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
             }
-            PROF_MARK(12);
         }
     }
     return waited;
@@ -586,18 +533,27 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     };
     int stage = 0;
     issue_tile(0, row, v0, nvt);
-    PROF_MARK(0);
 
     // ---- the place of this call among the calls that share its workspace (the first tile is on its
-    // way meanwhile).  Every CTA draws an arrival ticket; the next call is let in only after every
-    // CTA of this one has drawn (a barrier orders the draw before the signal), so the tickets of one
-    // call are `grid` consecutive numbers, which numbers the call.  Calls alternate between two sets
+    // way meanwhile).  Every CTA reads the workspace's call counter and then draws an arrival ticket;
+    // the CTA that draws the last ticket of the call advances the counter.  The next call is let in
+    // only after every CTA of this one has drawn (a barrier orders the draw before the signal), so
+    // all CTAs of a call read the same number, whatever the grids of the calls.  Calls alternate between two sets
     // of scratch lists and arrival counters, so a call never waits for the row merges of the call
     // right before it, only for those of the call before that.
     // CLUSTER (the CTAs of one row form a thread-block cluster and hand their parts over in shared
     // memory) is used for calls that wait for their predecessor at once: nothing to number. ----
-    if (!CLUSTER && tid == 0)
-        s_epoch = static_cast<uint32_t>(atomicAdd(p.arrivals, 1ull) / grid);
+    if (!CLUSTER && tid == 0) {
+        unsigned int e, t;
+        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(p.epoch_word) : "memory");
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(p.arrive_word) : "memory");
+        if (t == grid - 1u) {  // the last CTA of this call to arrive numbers the next call
+            *p.arrive_word = 0u;
+            const unsigned int n = e + 1u;
+            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(n) : "memory");
+        }
+        s_epoch = e;
+    }
 
     // ---- state of the current row part ----
     // Threshold groups: gs lanes form a group; the minimum over all groups (of full warps) of the group
@@ -732,6 +688,15 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
                 for (int e = 0; e < EPV; e++)
                     s_t += ex2_approx((f[e] - m_t) * c1);
             }
+        } else {
+            // Nothing is summed here (no sum wanted, or no finite reference yet), and the maxima pass
+            // NaN over: look for it and poison the sum, which sends the part to the exact fallback.
+            bool has_nan = false;
+#pragma unroll
+            for (int j = 0; j < VECS; j++)
+                has_nan |= Elem<T>::vector_has_nan(d[j]);
+            if (has_nan)
+                s_t = __int_as_float(0x7FC00000);
         }
 
         // ---- threshold refresh from the running thread maxima: on tiles 0, 1, 3, 7, ... of the part and
@@ -892,9 +857,9 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     plan->cluster = (!overlapping && parts_per_row >= 1 && parts_per_row <= kStreamMaxCluster) ? parts_per_row : 0;
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
-    // one arrival counter for the workspace; per row: an arrival counter for each of the two sets of
-    // lists and the number of calls that have written the row's result
-    plan->counters_bytes = 256 + ((static_cast<size_t>(d.rows) * 3 * 4 + 255) / 256) * 256;
+    // per row: an arrival counter for each of the two sets of lists (the call counter and the rows'
+    // counters of finished calls sit in the head of the workspace that the streaming kernels share)
+    plan->counters_bytes = ((static_cast<size_t>(d.rows) * 2 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
     plan->smem_bytes = 2 * static_cast<size_t>(threads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamSlots) * threads * 8;
     return VKOP_OK;
@@ -946,7 +911,7 @@ static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStr
 }
 
 int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const void *logits, void *out_values,
-                  void *out_indices, void *packets_out, void *workspace, int need_sum, cudaStream_t stream) {
+                  void *out_indices, void *packets_out, void *common_ws, void *workspace, int need_sum, cudaStream_t stream) {
     if (d.rows == 0)
         return VKOP_OK;
     ChunkParams p = {};
@@ -966,8 +931,10 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.index_offset = d.index_offset;
     p.out_values = out_values;
     p.out_indices = out_indices;
-    p.arrivals = reinterpret_cast<unsigned long long *>(workspace);
-    p.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(workspace) + 256);
+    p.arrive_word = reinterpret_cast<unsigned int *>(common_ws);
+    p.epoch_word = reinterpret_cast<unsigned int *>(static_cast<char *>(common_ws) + 4);
+    p.row_done = reinterpret_cast<unsigned int *>(static_cast<char *>(common_ws) + 256);
+    p.counters = reinterpret_cast<unsigned int *>(workspace);
     p.lists = reinterpret_cast<unsigned long long *>(static_cast<char *>(workspace) + plan.counters_bytes);
     p.packets_out = reinterpret_cast<uint32_t *>(packets_out);
     p.nvv = plan.nvv;
@@ -975,10 +942,6 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.vstride = plan.vstride;
     p.parts_per_row = plan.parts_per_row;
     p.input_ready = (d.flags & VKOP_FLAG_INPUT_READY) ? 1 : 0;
-#ifdef VKOP_PHASE_PROF
-    static int prof_calls = 0;
-    p.prof_seq = prof_calls++;
-#endif
     if (plan.aligned && reinterpret_cast<uintptr_t>(logits) % 16 != 0)
         return VKOP_INVALID_ARG;  // planned for an aligned base
 #define VKOP_STREAM(T) (plan.aligned ? launch_stream_t<T, true>(p, plan, stream) : launch_stream_t<T, false>(p, plan, stream))
@@ -993,8 +956,3 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
 
 }  // namespace vkop_cuda
 
-#ifdef VKOP_PHASE_PROF
-extern "C" int vkop_debug_read_phase_prof(unsigned long long *host, size_t count) {
-    return cudaMemcpyFromSymbol(host, vkop_cuda::g_phase_prof, count * sizeof(unsigned long long)) == cudaSuccess ? 0 : -4;
-}
-#endif
