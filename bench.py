@@ -317,7 +317,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llm_vocab_f32", choices=sorted(WORKLOADS) + ["yolo_nms"])
     ap.add_argument("--splits", type=int, default=0, help="chunks per row (0 = automatic)")
-    ap.add_argument("--path", default="auto", choices=["auto", "chunk", "stream", "radix"])
+    ap.add_argument("--path", default="auto", choices=["auto", "chunk", "stream", "radix", "bulk"])
     ap.add_argument("--serialize", action="store_true",
                     help="do not declare the resident inputs ready: every launch fully waits for the one before")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -366,7 +366,7 @@ def main():
     bufs = [h.to(dev) for h in host]
     values = torch.empty((rows, k), dtype=dtype, device=dev)
     indices = torch.empty((rows, k), dtype=torch.int32, device=dev)
-    path = {"auto": capi.PATH_AUTO, "chunk": capi.PATH_CHUNK, "stream": capi.PATH_STREAM, "radix": capi.PATH_RADIX}[args.path]
+    path = {"auto": capi.PATH_AUTO, "chunk": capi.PATH_CHUNK, "stream": capi.PATH_STREAM, "radix": capi.PATH_RADIX, "bulk": capi.PATH_BULK}[args.path]
     # the inputs of every step are resident and complete before the timed region starts
     flags = 0 if args.serialize else capi.FLAG_INPUT_READY
     desc = capi.make_desc(bufs[0], k, inv_t, splits=args.splits, path=path, flags=flags)

@@ -54,8 +54,9 @@ typedef enum vkop_select_path {
     VKOP_PATH_CHUNK = 1,  /* one CTA per chunk of a row, the chunk held in registers */
     VKOP_PATH_RADIX = 2,  /* multi-pass radix select (large k, very long rows) */
     VKOP_PATH_STREAM = 3, /* persistent CTAs streaming cp.async tiles with a running threshold (any alignment) */
-    VKOP_PATH_BULK = 4    /* persistent CTAs fed by bulk copies into a shared-memory ring: long rows that start on
-                             16-byte boundaries; AUTO prefers it where it applies */
+    VKOP_PATH_BULK = 4    /* streaming CTAs fed by bulk copies (cp.async.bulk + mbarrier) into a shared-memory ring,
+                             selection in a second small kernel: long rows that start on 16-byte boundaries.
+                             Chosen by name only: AUTO does not pick it */
 } vkop_select_path;
 
 /* The logits are complete and visible before the call is enqueued: no earlier
@@ -85,7 +86,8 @@ int vkop_cuda_workspace_init(void *workspace, size_t bytes, void *stream);
  * (core/runtime.cpp:480-520).
  *
  * Selection is on the stored logit: value descending, lower index first among
- * equal values (-0 equals +0, NaN ranks above +inf).  Output values are the
+ * equal values (-0 equals +0; NaN is the largest value: first among the largest,
+ * last among the smallest).  Output values are the
  * softmax probabilities of x * inv_temperature (or the raw logits), in the
  * logits' dtype; indices are int32 (as the reference) or int64 (ONNX).
  * Outputs are [rows, k], row-major, sorted best first. */

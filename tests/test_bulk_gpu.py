@@ -28,14 +28,35 @@ def test_bulk_llm_vocab(capi, dtype):
     util.check_fused(x, workloads.LLM_K, workloads.LLM_INV_TEMPERATURE, what=f"bulk C3 {dtype}", path=capi.PATH_BULK)
 
 
-def test_bulk_is_the_automatic_choice(capi):
+@pytest.mark.parametrize("parts", [1, 2, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bulk_parts_per_row(capi, parts, dtype):
+    """Every row is cut into `parts` streaming CTAs (desc.splits names the number); ragged row ends, ties
+    across the parts of a row, k up to 128."""
+    g = torch.Generator().manual_seed(76 + parts)
+    epv = 4 if dtype == torch.float32 else 8
+    for rows, cols, k in [(5, 70001, 50), (33, 131072 + 8, 128), (64, 128256, 1)]:
+        if (cols + epv - 1) // epv // parts < 2048:
+            continue
+        stride = (cols + epv - 1) // epv * epv
+        buf = torch.randn(rows * stride, generator=g).to(dtype)
+        x_cpu = buf.view(rows, stride)[:, :cols]
+        x_cpu[0, : cols // 2] = x_cpu[0, cols - cols // 2:]  # every value of row 0 twice, in different parts
+        xg = buf.cuda().view(rows, stride)[:, :cols]
+        vals, idx = capi.softmax_topk(xg, k, 1.25, path=capi.PATH_BULK, splits=parts)
+        wv, wi = util.oracle_softmax_topk(x_cpu.contiguous(), k, 1.25)
+        util.assert_indices_equal(idx, wi, f"{parts} parts: {rows}x{cols} {dtype}")
+        util.assert_probs_close(vals, wv, dtype, f"{parts} parts: {rows}x{cols} {dtype}")
+
+
+def test_bulk_agrees_with_the_other_paths(capi):
     x = workloads.llm_vocab().cuda()
     a = capi.softmax_topk(x, 50, 1.25)
     b = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_BULK)
-    c = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_STREAM)
+    c = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_CHUNK)
     torch.cuda.synchronize()
-    assert torch.equal(a[1], b[1]) and torch.equal(a[0], b[0])
-    assert torch.equal(a[1], c[1])
+    assert torch.equal(a[1], b[1]) and torch.equal(a[1], c[1])
+    assert torch.allclose(a[0], b[0], rtol=1e-5, atol=1e-7)
 
 
 def test_bulk_vocab_sharded_shape_all_rows(capi):
@@ -168,8 +189,9 @@ def test_bulk_overlapping_calls(capi, rows, cols, k, dtype):
 
 
 def test_aligned_and_unaligned_pointers_share_a_workspace(capi):
-    """The same descriptor with a 16-byte aligned and an unaligned logits pointer runs two different kernels;
-    they may alternate on one workspace, overlapping, with one output buffer."""
+    """The same descriptor with a 16-byte aligned and an unaligned logits pointer gets two different launch
+    plans of the streaming kernel (another grid); the calls may alternate on one workspace, overlapping, with
+    one output buffer."""
     g = torch.Generator().manual_seed(75)
     rows, cols, k = 48, 66000, 20
     base = torch.randn(rows * cols + 8, generator=g)

@@ -18,6 +18,8 @@ SOURCES = ["capi.cu", "softmax_topk.cu", "softmax_topk_stream.cu", "softmax_topk
            "peer_exchange.cu", "sample.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wextra", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+# extra defines for tuning builds, e.g. VKOP_NVCC_DEFINES="-DVKOP_BULK_STAGES=5 -DVKOP_BULK_CTAS_PER_SM=2"
+NVCC_FLAGS += os.environ.get("VKOP_NVCC_DEFINES", "").split()
 
 
 def _nvcc() -> str:

@@ -51,11 +51,12 @@ static int plan_select(const vkop_softmax_topk_desc &d, const void *in, SelectPl
     // rows longer than one CTA's register tile, and enough of them: the streaming kernel
     const bool prefer_stream = row_bytes > 64 * 1024 && d.rows * row_bytes >= (2ll << 20);
     if (d.path == VKOP_PATH_STREAM || d.path == VKOP_PATH_BULK || (d.path == VKOP_PATH_AUTO && prefer_stream && d.splits == 0)) {
-        // Two kernels serve this kind: the bulk-copy kernel for 16-byte aligned long rows, the cp.async
-        // kernel for everything else.  Both number their calls in one shared head of the workspace, and
-        // each has its own part behind it, so calls with aligned and unaligned pointers may alternate.
+        // Two implementations serve this kind: the cp.async kernel (any alignment) and the bulk-copy
+        // kernels (16-byte aligned long rows).  Both number their calls in one shared head of the
+        // workspace, and each has its own part behind it.
         const bool base_aligned = reinterpret_cast<uintptr_t>(in) % 16 == 0;
-        const bool want_bulk = d.path != VKOP_PATH_STREAM, want_stream = d.path != VKOP_PATH_BULK;
+        // (the bulk-copy kernels are chosen by name only: measured, they do not beat the cp.async kernel yet)
+        const bool want_bulk = d.path == VKOP_PATH_BULK, want_stream = d.path != VKOP_PATH_BULK;
         const int rcb = want_bulk ? plan_bulk(d, in ? base_aligned : true, &plan->bulk) : VKOP_UNSUPPORTED;
         size_t stream_bytes = 0;
         rc = want_stream ? plan_stream(d, base_aligned, &plan->stream) : VKOP_UNSUPPORTED;
@@ -68,7 +69,7 @@ static int plan_select(const vkop_softmax_topk_desc &d, const void *in, SelectPl
         if (rc == VKOP_OK || rcb == VKOP_OK) {
             plan->kind = kSelectStream;
             plan->use_bulk = rcb == VKOP_OK;
-            const size_t bulk_bytes = rcb == VKOP_OK ? plan->bulk.counters_bytes + plan->bulk.lists_bytes : 0;
+            const size_t bulk_bytes = rcb == VKOP_OK ? plan->bulk.scratch_bytes : 0;
             plan->bulk_off = stream_common_bytes(d.rows);
             plan->stream_off = plan->bulk_off + bulk_bytes;
             plan->bytes = plan->stream_off + stream_bytes;

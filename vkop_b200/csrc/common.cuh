@@ -36,6 +36,13 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     return (x != x) ? 0xFFFFFFFFu : k;
 }
 
+// Key of an element AFTER the sign flip that turns "smallest" into "largest" (flipped != 0): the
+// flip leaves a NaN a NaN, which must then rank last, not first (NaN is the largest value whichever
+// way the selection goes): key 1 lies below the key of -inf, and no number maps to it.
+__device__ __forceinline__ uint32_t order_key_sel(float x, int flipped) {
+    return (flipped && x != x) ? 1u : order_key(x);
+}
+
 __device__ __forceinline__ float key_to_float(uint32_t k) {
     uint32_t u = (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k;
     return __uint_as_float(u);

@@ -40,13 +40,13 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
 
 // ---- bulk-copy streaming path (softmax_topk_bulk.cu): long, 16-byte aligned rows ----
 struct BulkPlan {
-    int grid;
-    int64_t per_cta, nvv, vstride;
-    int maxparts, list_cap;
-    size_t counters_bytes, lists_bytes, smem_bytes;
+    int grid;      // CTAs of the streaming kernel: rows * parts
+    int parts;     // parts (CTAs) per row
+    int64_t nvv, vstride;
+    size_t scratch_bytes, smem_bytes;
 };
-// Head of a workspace of the streaming kernels, shared by both: call counter, arrival counter and
-// status word (256 bytes), then one counter of finished calls per row.
+// Head of a workspace of the streaming kernels, shared by all of them: call counters, arrival counters
+// and status word (256 bytes), then one counter of finished calls per row.
 size_t stream_common_bytes(int64_t rows);
 int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan);
 int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const void *logits, void *out_values, void *out_indices,

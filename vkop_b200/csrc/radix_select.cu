@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kRadixThreads) radix_hist_kernel(const RadixPa
         for (int e = 0; e < EPV; e++) {
             const int64_t i = ibase + e;
             if (!ragged || (i >= 0 && i < p.cols)) {
-                const unsigned long long c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                const unsigned long long c = make_cand(order_key_sel(f[e], p.negate), static_cast<uint32_t>(i));
                 if ((c & mask) == prefix)
                     atomicAdd(&s_hist[static_cast<unsigned>(c >> shift) & (nbins - 1)], 1);
             }
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kRadixThreads) radix_collect_kernel(const Radi
         for (int e = 0; e < EPV; e++) {
             const int64_t i = ibase + e;
             if (i >= 0 && i < p.cols) {
-                const unsigned long long c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                const unsigned long long c = make_cand(order_key_sel(f[e], p.negate), static_cast<uint32_t>(i));
                 if (c >= thr) {
                     const int pos = atomicAdd(&p.cand_count[row], 1);
                     if (pos < p.k)

@@ -227,7 +227,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
             for (int e = 0; e < EPV; e++) {
                 int64_t i = v * EPV + e - head;
                 if (i >= 0 && i < cols) {
-                    uint64_t c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                    uint64_t c = make_cand(order_key_sel(f[e], negate), static_cast<uint32_t>(i));
                     if ((c & mask) == prefix)
                         atomicAdd(&s_hist[static_cast<int>(c >> shift) & 255], 1);
                 }
@@ -268,7 +268,7 @@ __device__ __noinline__ void select_fallback(const uint4 *vbase, int64_t v0, int
         for (int e = 0; e < EPV; e++) {
             int64_t i = v * EPV + e - head;
             if (i >= 0 && i < cols) {
-                uint64_t c = make_cand(order_key(f[e]), static_cast<uint32_t>(i));
+                uint64_t c = make_cand(order_key_sel(f[e], negate), static_cast<uint32_t>(i));
                 if (c >= prefix) {
                     int pos = atomicAdd(s_count, 1);
                     if (pos < kCandCap)
@@ -310,14 +310,15 @@ __device__ __noinline__ void merge_lists(const ChunkParams &p, int64_t row, cons
             unsigned long long h0, h1;
             if (PEERS) {
                 const unsigned long long *L = cooperative_groups::this_cluster().map_shared_rank(lists, g);
+                // header and the whole capacity in one round trip (entries past the count are ignored)
                 h0 = L[0];
                 h1 = L[1];
-                cnt = static_cast<int>(h1 & 0xFFFFu);
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const int i = lane + 32 * j;
-                    regs[j] = i < cnt ? L[2 + i] : 0ull;
+                    regs[j] = i < p.list_cap ? L[2 + i] : 0ull;
                 }
+                cnt = static_cast<int>(h1 & 0xFFFFu);
             } else {
                 const unsigned long long *L = lists + g * stride;
                 h0 = __ldcg(L);

@@ -1,36 +1,43 @@
-// Fused Softmax + TopK, bulk-copy streaming path: the kernel for long, 16-byte aligned rows.
+// Fused Softmax + TopK, bulk-copy streaming path: two kernels for long, 16-byte aligned rows.
 //
-// Data movement.  Every CTA owns one contiguous range of 16-byte vector slots of the [rows, cols]
-// tensor (byte-balanced over the grid, one CTA per SM, ranges may run across rows).  One elected
-// thread of a producer warp walks the range in tiles of kTileVecs vectors and hands every tile to
-// the copy engine with a single bulk copy (cp.async.bulk.shared::cluster.global, plain form: no
-// multicast, the source is this GPU's own memory) into a ring of shared-memory stages; every stage
-// has a "full" mbarrier that the copy completes (expect-tx / complete-tx bytes) and an "empty"
-// mbarrier that the consumer warps arrive at once they hold the tile in registers.  The consumer
-// threads issue no copy, compute no address and wait only on the full barrier.
+// Kernel 1, bulk_stream_kernel, reads every logit once.  Every row is cut into P equal parts, one
+// CTA each (P chosen so that the parts of one call fill the GPU about twice).  Inside a CTA every
+// consumer warp has its own ring of shared-memory stages and takes tiles warp, warp + W, ... of the
+// part (a tile is 2 KB: four 16-byte vectors per lane).  A producer warp hands the tiles to the copy
+// engine, lane w feeding the ring of consumer warp w with one bulk copy per tile
+// (cp.async.bulk.shared::cluster.global, plain form: no multicast, the source is this GPU's own
+// memory); every stage has a "full" mbarrier that the copy completes (expect-tx / complete-tx bytes)
+// and an "empty" mbarrier at which the consumer warp arrives once it holds the tile in registers.
+// Consumer warps issue no copy, compute no address, and never wait for one another inside a part
+// except once, after their first tile.
 //
-// Per tile and consumer thread: four 16-byte shared-memory loads, the maximum of the 16 (or 32)
+// Per tile and consumer lane: four 16-byte shared-memory loads, the maximum of the 16 (or 32)
 // elements, and the exp-sum against a per-thread offset o = -(m * c1): one FFMA, one ex2 and one add
 // per element (the offset moves, and the sum is rescaled, only when the thread's maximum rises).
 //
 // Selection.  Any value that at least k thread maxima reach bounds the k-th largest element of the
-// row part from below.  The thread maxima live in shared memory as order-preserving keys; the
-// bound T is found by a warp-level bisection over them: once after the first tile of a part (all
-// consumers wait for it), then on tiles 1, 3, 7, ... by one consumer warp in turn while the others
-// keep streaming.  In the loop a thread only tests the maximum of its 16 elements against T; when
-// it reaches T the thread records where it is (one predicated 32-bit shared-memory store, no
-// branch).  At the end of the part the recorded groups (a few hundred) are read again from L2,
-// filtered by the final bound and ranked.
+// part from below.  Every warp takes the r-th largest of its 32 running thread maxima
+// (r = ceil(k / warps)); the smallest of those over the warps is such a value.  The warps post theirs
+// after their first tile of the part (one barrier: the first bound) and again after their tiles 1,
+// 3, 7, ... (no barrier: whoever posts recomputes the minimum and raises the shared bound).  In the
+// loop a lane only tests the maximum of its elements of the tile against the bound; a vector that
+// reaches it goes to a pool in shared memory as it is, with its place in the row.  At the end of the
+// part the CTA writes the pool (a few hundred vectors), the part's maximum, exp-sum and bound to
+// scratch memory and is gone: the streaming CTAs do nothing that is not streaming.
 //
-// Rows cut across CTAs: every part publishes (max, sum, bound, candidates) to scratch memory; the
-// last part of a row to arrive (ticket counter) merges the row and writes its result.  Launches use
-// programmatic stream serialization as the other streaming kernel does: with
-// VKOP_FLAG_INPUT_READY consecutive calls overlap, scratch lists alternate between two sets by call
-// parity and a per-row counter of finished calls orders results and list reuse.
+// Kernel 2, bulk_select_kernel, one small CTA per row, launched behind kernel 1 with programmatic
+// stream serialization: it lets the next call's kernel 1 in at once, waits for its own kernel 1,
+// reads the row's pools (from L2), keeps the elements that reach the largest of the parts' bounds,
+// tightens the bound once more on the candidates themselves, ranks the survivors by counting and
+// writes the k results.  It runs beside the next call's streaming CTAs.
 //
-// Every wait on an mbarrier is bounded (about a second); a wait that runs out sets an abort flag and
-// VKOP_TIMEOUT in the workspace status word, the CTA stops issuing copies, waits (bounded) for the
-// copies in flight and returns.
+// With VKOP_FLAG_INPUT_READY consecutive calls overlap: the scratch pools are used in turn (kBulkSets sets), and a per-row counter of finished calls keeps the results of a row in call order
+// and tells when a set may be written again.  Calls number themselves on the device.
+//
+// Every wait in these kernels is bounded (about a second): a wait that runs out sets an abort flag
+// and VKOP_TIMEOUT in the workspace status word; the CTA stops issuing copies, walks on without
+// data so that its warps still meet at their barriers, waits (bounded) for the copies in flight and
+// returns.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -40,17 +47,30 @@
 
 namespace vkop_cuda {
 
-constexpr int kBulkConsumers = 256;                 // consumer threads (8 warps)
-constexpr int kBulkThreads = kBulkConsumers + 32;   // plus the producer warp
-constexpr int kBulkTileVecs = 1024;                 // 16 KB per tile
-constexpr int kBulkStages = 5;                      // 80 KB ring
+#ifndef VKOP_BULK_STAGES
+#define VKOP_BULK_STAGES 3
+#endif
+#ifndef VKOP_BULK_TILE_VECS
+#define VKOP_BULK_TILE_VECS 1024
+#endif
+#ifndef VKOP_BULK_CTAS_PER_SM
+#define VKOP_BULK_CTAS_PER_SM 2
+#endif
+constexpr int kBulkConsumers = 256;                 // consumer threads of a streaming CTA (8 warps)
+constexpr int kBulkWarps = kBulkConsumers / 32;
+constexpr int kBulkThreads = kBulkConsumers + 64;   // plus the producer warp and the control warp
+constexpr int kBulkTileVecs = VKOP_BULK_TILE_VECS;  // a tile: 16 KB, one bulk copy, consumed by all consumer warps
+constexpr int kBulkStages = VKOP_BULK_STAGES;       // tiles in the ring (48 KB)
 constexpr int kBulkJ = kBulkTileVecs / kBulkConsumers;  // vectors per consumer thread and tile
-constexpr int kBulkSlots = 4;                       // private record slots per consumer thread
-constexpr int kBulkOverflow = 256;                  // shared overflow records
-constexpr int kBulkRegion = 1024;                   // 64-bit slots of each of the two work regions
-constexpr int kBulkMaxParts = 56;                   // most CTAs one row may be cut across
+constexpr int kBulkPool = 1024;                     // vectors the pool of a part holds
+constexpr int kBulkMaxParts = 8;                    // most parts a row is cut into
+constexpr int kBulkMinPartVecs = 2048;              // a part is at least 32 KB
+constexpr int kBulkSets = 4;                        // sets of scratch pools that consecutive calls use in turn
+constexpr int kSelThreads = 256;                    // threads of a selecting CTA
+constexpr int kSelCap = 1024;                       // candidates a row may gather before the exact fallback takes over
 constexpr int kBar = 1;                             // named barrier of the consumer threads
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
+static_assert(kBulkJ >= 1 && kBulkJ <= 8 && kBulkJ * kBulkConsumers == kBulkTileVecs, "every consumer thread takes the same share of a tile");
 
 // ---- mbarrier / bulk copy wrappers (shared-memory addresses as 32-bit) ----
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -63,11 +83,24 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// may suspend the thread for a while when the phase is not complete
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// never suspends
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -79,15 +112,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Waits for the phase with the given parity; false when the limit ran out (then *abort is set).
+// Waits for the phase with the given parity; false when the limit ran out (then *abort is set) or
+// somebody else has given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
-    if (mbar_test(bar, parity))
+    if (mbar_try(bar, parity))
         return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 256; i++) {
-            if (mbar_test(bar, parity))
+            if (mbar_try(bar, parity))
                 return true;
         }
         if (*abort)
@@ -104,659 +138,644 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
                  : "memory");
 }
 
-// Maximum of three floats (NaN operands are passed over, as fmaxf does).
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
+// What a part leaves in scratch memory for the selecting kernel: a header, then the pooled vectors,
+// then the place of each in its row (vector index).
+struct PartHeader {
+    float mz;        // part maximum of z = x * inv_t
+    float sum;       // exp-sum of the part relative to mz
+    uint32_t tkey;   // bound: at least k elements of the part reach it (0: none)
+    int32_t count;   // pooled vectors, or -1: the pool is no use (NaN, or more vectors than it holds)
+    uint32_t epoch;  // number of the call on its workspace
+    uint32_t pad[3];
+};
+constexpr size_t kPartStride = sizeof(PartHeader) + static_cast<size_t>(kBulkPool) * 20;
+static_assert(sizeof(PartHeader) == 32 && kPartStride % 16 == 0, "pooled vectors are stored as 16-byte words");
 
 struct BulkParams {
-    ChunkParams c;            // shared with the selection helpers (logits, shape, outputs, lists, counters)
+    ChunkParams c;            // logits, shape, outputs; nvv, vstride, per_cta; parts_per_row = P
     int *status;              // workspace: VKOP_OK or VKOP_TIMEOUT
-    int trigger_tile;         // tile after which the CTA lets the next call of the stream in
-    int debug;                // TEMPORARY: experiment switches
+    unsigned int *epoch2, *arrive2;  // workspace: call counter and arrival counter of the selecting kernel
+    unsigned char *scratch;   // [kBulkSets][rows * P] parts of kPartStride bytes
 };
 
-// Walks the tiles of a CTA's range: tiles never cross a row and never exceed kBulkTileVecs vectors.
-struct TileWalk {
-    uint32_t nvv;
-    int row, v0, nv, remaining;
-    bool part_first, part_last;
-    __device__ __forceinline__ void start(uint32_t Vs, uint32_t Ve, uint32_t nvv_) {
-        nvv = nvv_;
-        row = static_cast<int>(Vs / nvv);
-        v0 = static_cast<int>(Vs - static_cast<uint32_t>(row) * nvv);
-        remaining = static_cast<int>(Ve - Vs);
-        part_first = true;
-        shape();
-    }
-    __device__ __forceinline__ void shape() {
-        const int left = static_cast<int>(nvv) - v0;
-        nv = kBulkTileVecs < left ? kBulkTileVecs : left;
-        if (nv > remaining)
-            nv = remaining;
-        part_last = (v0 + nv == static_cast<int>(nvv)) || (nv == remaining);
-    }
-    // moves to the next tile; false when the range is exhausted
-    __device__ __forceinline__ bool next() {
-        remaining -= nv;
-        if (remaining <= 0)
-            return false;
-        part_first = part_last;
-        v0 += nv;
-        if (v0 >= static_cast<int>(nvv)) {
-            row++;
-            v0 = 0;
-        }
-        shape();
-        return true;
-    }
+// Control block of a streaming CTA, behind the arrays in dynamic shared memory.
+struct BulkCtl {
+    uint64_t full[kBulkStages], empty[kBulkStages];
+    float red[kBulkWarps];
+    uint32_t wr[kBulkWarps];  // per warp: the r-th largest of its running thread maxima, as a key
+    uint32_t wm[kBulkWarps];  // per warp: its largest thread maximum (end of the part)
+    int nrec;                 // vectors in the pool (may count past its capacity)
+    int nan_seen;
+    uint32_t tkey;            // bound of the part as a key (0: none)
+    uint32_t epoch;           // number of this call on its workspace
+    int epoch_ready;          // the control warp has drawn it
+    int abort;
+    int pad[2];
 };
 
-// Largest key v such that at least k of the 256 keys reach it (0: fewer than k keys are set), by
-// bisection between `lo` (0, or a key already known to be reached by k keys) and the largest key.
-// Executed by one warp; the keys only grow while it runs, which keeps any answer valid.
-__device__ __noinline__ uint32_t bulk_bisect(const volatile uint32_t *keys, int k, uint32_t lo, int iters) {
+// Dynamic shared memory of the streaming kernel: tile rings | pool of recorded vectors | their places | control.
+extern __shared__ __align__(128) unsigned char s_bulk[];
+constexpr size_t kOffPool = static_cast<size_t>(kBulkStages) * kBulkTileVecs * 16;
+constexpr size_t kOffPoolV = kOffPool + static_cast<size_t>(kBulkPool) * 16;
+constexpr size_t kOffCtl = kOffPoolV + static_cast<size_t>(kBulkPool) * 4;
+constexpr size_t kBulkSmemBytes = kOffCtl + sizeof(BulkCtl);
+static_assert(kOffCtl % 16 == 0, "the control block holds 64-bit barriers");
+
+// The r-th largest of the warp's 32 keys (0 when fewer than r keys are set).
+__device__ __forceinline__ uint32_t warp_rth_largest(uint32_t key, int r) {
     const int lane = threadIdx.x & 31;
-    uint32_t kv[kBulkConsumers / 32];
-    uint32_t hi = 0;
-    int set = 0;
-#pragma unroll
-    for (int i = 0; i < kBulkConsumers / 32; i++) {
-        kv[i] = keys[lane + 32 * i];
-        hi = kv[i] > hi ? kv[i] : hi;
-        set += kv[i] != 0u ? 1 : 0;
+    uint32_t cur = key, rth = 0;
+    for (int i = 0; i < r; i++) {
+        rth = __reduce_max_sync(kFullMask, cur);
+        const unsigned b = __ballot_sync(kFullMask, cur == rth);
+        if (lane == __ffs(b) - 1)
+            cur = 0;
     }
-    hi = __reduce_max_sync(kFullMask, hi);
-    set = __reduce_add_sync(kFullMask, set);
-    if (set < k)
-        return 0u;
-    if (lo == 0u)
-        lo = 1u;
-    for (int it = 0; it < iters && hi > lo; it++) {
-        const uint32_t mid = lo + ((hi - lo + 1u) >> 1);
-        int c = 0;
-#pragma unroll
-        for (int i = 0; i < kBulkConsumers / 32; i++)
-            c += kv[i] >= mid ? 1 : 0;
-        c = __reduce_add_sync(kFullMask, c);
-        if (c >= k)
-            lo = mid;
-        else
-            hi = mid - 1u;
-    }
-    return lo;
+    return rth;
 }
 
-// Pointers into the CTA's shared memory.
-struct BulkShared {
-    uint4 *tiles;               // kBulkStages stages of kBulkTileVecs vectors
-    uint64_t *ra, *rb;          // two work regions of kBulkRegion 64-bit slots, contiguous
-    uint32_t *rec;              // (kBulkSlots + 1) x kBulkConsumers private records (the last row is a dummy)
-    uint32_t *ovf;              // shared overflow records
-    volatile uint32_t *keys;    // running thread maxima of the current part as order keys (0: none)
-    int *hist, *sint, *tmp, *pick, *count, *flag;
-    float *red;
-    int *nrec, *novf, *ncand;   // compacted records, overflow records, candidates
-    uint32_t *tkey;             // bound of the current part as a key (0: none)
-    volatile int *abort;
-};
-
-// What the end of a row part needs from the streaming loop.
-struct BulkPartEnd {
-    float m_t, o_t, s_t;   // this thread's maximum, exponent offset and exp-sum against that offset
-    int cnt;               // groups this thread recorded
-    bool nan_seen;         // (selection without a sum) the thread met a NaN
-    int row, part_v0, part_v1;
-    uint32_t epoch;
-    bool waited;
-};
-
-// End of a row part, executed by the consumer threads: statistics, expansion of the recorded groups
-// into candidates, then selection (the part is a whole row) or publication and, for the last part
-// of the row to arrive, the merge of the row.  Returns whether the CTA has waited for the previous
-// call by now.
-template <typename T>
-__device__ __noinline__ bool bulk_finish_part(const BulkParams &bp, const BulkShared &sh, const BulkPartEnd e) {
-    constexpr int EPV = Elem<T>::kPerVec;
-    constexpr int NC = kBulkConsumers;
-    constexpr int NW = NC / 32;
-    const ChunkParams &p = bp.c;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t grid = gridDim.x;
-    const uint32_t nvv = static_cast<uint32_t>(p.nvv);
-    const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
-    const uint32_t per = static_cast<uint32_t>(p.per_cta);
-    const int cols = static_cast<int>(p.cols);
-    const float c1 = p.inv_t * kLog2e;
-    const int64_t lstride = 2 + p.list_cap;
-    const int row = e.row;
-    const uint32_t epoch = e.epoch;
-    const int64_t set = epoch & 1u;
-    const uint4 *const vbase = reinterpret_cast<const uint4 *>(p.logits) + static_cast<int64_t>(row) * p.vstride;
-    const bool whole = e.part_v0 == 0 && e.part_v1 == static_cast<int>(nvv);
-    bool waited = e.waited;
-
-    // Has the call before the previous one finished with this row (its lists are about to be
-    // overwritten), has the previous call written the row's result?  Asked early, used later.
-    unsigned int done_calls = 0;
-    if (tid == 0) {
-        if (!waited)
-            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(done_calls) : "l"(p.row_done + row) : "memory");
-        sh.flag[0] = whole ? done_calls == epoch : static_cast<int>(done_calls - epoch + 1u) >= 0;
-    }
-    if (e.nan_seen)
-        sh.flag[2] = 1;
-    cta_sync<kBar, NC>();  // #1: keys, records and the overflow count are final
-
-    // ---- statistics (every warp reduces the 256 keys itself: no second barrier for the maximum) ----
-    uint32_t mkey = 0;
+// The smallest of the warps' posted keys (0: some warp has posted none yet).
+template <int NW>
+__device__ __forceinline__ uint32_t posted_bound(const uint32_t *posted) {
+    const volatile uint32_t *wr = posted;
+    uint32_t t = 0xFFFFFFFFu;
 #pragma unroll
-    for (int i = 0; i < NC / 32; i++) {
-        const uint32_t kv = sh.keys[lane + 32 * i];
-        mkey = kv > mkey ? kv : mkey;
+    for (int q = 0; q < NW; q++) {
+        const uint32_t v = wr[q];
+        t = v < t ? v : t;
     }
-    mkey = __reduce_max_sync(kFullMask, mkey);
-    const float M = mkey ? key_to_float(mkey) : -INFINITY;  // part maximum of the stored logits
-    const float O = -__fmul_rn(M, c1);
-    {
-        const float contrib = (e.m_t == -INFINITY && e.s_t == e.s_t) ? 0.0f : e.s_t * ex2_approx(O - e.o_t);
-        const float ws = warp_sum(contrib);
-        if (lane == 0)
-            sh.red[warp] = ws;
-    }
-    // ---- the recorded groups go to one dense list (region B as 32-bit words) ----
-    uint32_t *const list = reinterpret_cast<uint32_t *>(sh.rb);
-    {
-        const int mine = e.cnt < kBulkSlots ? e.cnt : kBulkSlots;
-        int incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(kFullMask, incl, o);
-            if (lane >= o)
-                incl += v;
-        }
-        int base = 0;
-        if (lane == 31)
-            base = atomicAdd(sh.nrec, incl);
-        base = __shfl_sync(kFullMask, base, 31) + incl - mine;
-        for (int q = 0; q < mine; q++)
-            list[base + q] = sh.rec[q * NC + tid];
-    }
-    if (warp == 0) {
-        // the final bound: exact (the bisection runs until it closes)
-        const uint32_t t = bulk_bisect(sh.keys, p.k, *sh.tkey, 32);
-        if (lane == 0 && t > *sh.tkey)
-            *sh.tkey = t;
-    }
-    cta_sync<kBar, NC>();  // #2
-    float S = 0.0f;
-#pragma unroll
-    for (int w = 0; w < NW; w++)
-        S += sh.red[w];
-    // S is relative to the offset O = -rn(M * c1); the published sum is relative to M exactly
-    if (M != -INFINITY)
-        S *= ex2_approx(-__fmaf_rn(M, c1, O));
-    const float mz = __fmul_rn(M, p.inv_t);
-    uint32_t tpub = *sh.tkey;
-    const float Tf = tpub ? key_to_float(tpub) : -INFINITY;
-    const int n_rec = *sh.nrec;
-    const int novf = *sh.novf;
-    const int nvalid = (e.part_v1 * EPV < cols ? e.part_v1 * EPV : cols) - e.part_v0 * EPV;
-    const int kk = nvalid < p.k ? nvalid : p.k;
-    const bool bad = sh.flag[2] != 0 || novf > kBulkOverflow || (p.need_sum && S != S);
-    const uint32_t xmask = p.negate ? (sizeof(T) == 4 ? 0x80000000u : 0x80008000u) : 0u;
-
-    int C = kBulkRegion + 1;
-    if (!bad) {
-        // ---- expansion: every recorded group is kBulkJ vectors, re-read from L2 ----
-        const int ngroups = n_rec + novf;
-        const int nvec = ngroups * kBulkJ;
-        for (int base = 0; base < nvec; base += NC * 4) {
-            uint4 d[4];
-            int vv[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = base + u * NC + tid;
-                vv[u] = -1;
-                if (i < nvec) {
-                    const int g = i / kBulkJ;
-                    const uint32_t r = g < n_rec ? list[g] : sh.ovf[g - n_rec];
-                    const int v = static_cast<int>(r) + (i - g * kBulkJ) * NC;
-                    if (v < e.part_v1) {
-                        vv[u] = v;
-                        d[u] = __ldcg(vbase + v);
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                if (vv[u] < 0)
-                    continue;
-                d[u].x ^= xmask; d[u].y ^= xmask; d[u].z ^= xmask; d[u].w ^= xmask;
-                float f[EPV];
-                Elem<T>::unpack(d[u], f);
-#pragma unroll
-                for (int q = 0; q < EPV; q++) {
-                    const int idx = vv[u] * EPV + q;
-                    if (idx < cols && f[q] >= Tf) {
-                        const int pos = atomicAdd(sh.ncand, 1);
-                        if (pos < kBulkRegion)
-                            sh.ra[pos] = make_cand(order_key(f[q]), static_cast<uint32_t>(idx));
-                    }
-                }
-            }
-        }
-        cta_sync<kBar, NC>();  // #3
-        C = *sh.ncand;
-    }
-    if (C > kBulkRegion) {
-        // Rare: NaN in the part, threads that ran out of record slots, or more candidates than the
-        // region holds (massive ties).  Exact radix select over the part, re-read from L2; it works
-        // in both regions as one list.
-        cta_sync<kBar, NC>();
-        select_fallback<T, NC, kBar>(vbase, e.part_v0, e.part_v1, 0, p.cols, p.negate, kk, sh.ra, sh.count, sh.hist, sh.pick);
-        C = *sh.count;
-        tpub = 0;
-    }
-
-    if (whole) {
-        // ---- the part is the row: select and write.  Results of one row are written in call order. ----
-        if (!waited && !sh.flag[0]) {
-            if (tid == 0) {  // look once more before giving up
-                unsigned int dn;
-                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(p.row_done + row) : "memory");
-                sh.flag[1] = dn == epoch;
-            }
-            cta_sync<kBar, NC>();
-            if (!sh.flag[1]) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                waited = true;
-            }
-        }
-        if (p.packets_out && tid == 0) {
-            uint32_t *pk = p.packets_out + static_cast<int64_t>(row) * packet_words(p.k);
-            pk[0] = __float_as_uint(mz);
-            pk[1] = __float_as_uint(S);
-            pk[2] = static_cast<uint32_t>(C < p.k ? C : p.k);
-            pk[3] = 0;
-        }
-        select_and_emit<T, NC, kBar>(p, row, sh.ra, C, sh.rb, mz, S, nullptr, sh.tmp);
-        cta_sync<kBar, NC>();
-        if (tid == 0) {
-            const unsigned int d = epoch + 1u;
-            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.row_done + row), "r"(d) : "memory");
-        }
-        return waited;
-    }
-
-    // ---- publish the part; the last part of the row to arrive merges the row ----
-    const uint32_t c_first = stream_owner(static_cast<uint32_t>(row) * nvv, grid, per, nvv, total, 0u);
-    const int pidx = static_cast<int>(blockIdx.x - c_first);
-    unsigned long long *const rowlists = p.lists + (set * p.rows + row) * p.splits * lstride;
-    unsigned long long *const mylist = rowlists + pidx * lstride;
-    if (!waited && !sh.flag[0]) {  // rare: the row's lists may still be in use by the call before the previous one
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        waited = true;
-    }
-    if (C > p.list_cap) {
-        // more than a part may publish: its own best kk, ranked, go out instead
-        select_and_emit<T, NC, kBar>(p, row, sh.ra, C, sh.rb, 0.0f, 0.0f, mylist + 2, sh.tmp);
-        C = kk;
-        tpub = 0;
-    } else {
-        for (int i = tid; i < C; i += NC)
-            mylist[2 + i] = sh.ra[i];
-    }
-    cta_sync<kBar, NC>();
-    if (tid == 0) {
-        mylist[0] = (static_cast<unsigned long long>(__float_as_uint(S)) << 32) | __float_as_uint(mz);
-        mylist[1] = (static_cast<unsigned long long>(tpub) << 16) | static_cast<unsigned long long>(C);
-        const uint32_t c_end = stream_owner(static_cast<uint32_t>(row + 1) * nvv - 1u, grid, per, nvv, total, 0u);
-        const int nparts = static_cast<int>(c_end - c_first + 1u);
-        unsigned int arrived;
-        unsigned int *ticket = p.counters + set * p.rows + row;
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(ticket) : "memory");
-        const bool last = arrived == static_cast<unsigned int>(nparts - 1);
-        int in_order = 1;
-        if (last) {
-            *ticket = 0;  // ready for the next call that uses this set
-            unsigned int d;
-            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(d) : "l"(p.row_done + row) : "memory");
-            in_order = d == epoch;
-        }
-        sh.flag[1] = last ? nparts : 0;
-        sh.flag[0] = in_order;
-    }
-    cta_sync<kBar, NC>();
-    const int nparts = sh.flag[1];
-    if (nparts > 0) {
-        if (!waited && !sh.flag[0]) {  // rare: the previous call has not written this row yet
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            waited = true;
-        }
-        merge_lists<T, NC, false, kBar>(p, row, rowlists, lstride, nparts, sh.ra, sh.rb, sh.red, sh.sint, sh.tmp);
-        cta_sync<kBar, NC>();
-        if (tid == 0) {
-            const unsigned int d = epoch + 1u;
-            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.row_done + row), "r"(d) : "memory");
-        }
-    }
-    return waited;
+    return t;
 }
 
+// Waits (bounded, about a second) until the row's counter of finished calls satisfies the test:
+// exact: it shows `want`; otherwise: it has reached `want`.  The calls it waits for were launched
+// before this one and never wait for it.  Called by one thread.
+__device__ __noinline__ bool wait_row_counter(const unsigned int *row_done, uint32_t want, bool exact) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++) {
+            unsigned int dn;
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done) : "memory");
+            if (exact ? dn == want : static_cast<int>(dn - want) >= 0)
+                return true;
+            __nanosleep(64);
+        }
+        if (global_ns() - t0 > kWaitLimitNs)
+            return false;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Kernel 1: CTA c streams part c % P of row c / P.
 template <typename T>
-__global__ void __launch_bounds__(kBulkThreads, 2) softmax_topk_bulk_kernel(const BulkParams bp) {
+__global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stream_kernel(const __grid_constant__ BulkParams bp) {
     constexpr int EPV = Elem<T>::kPerVec;
     constexpr int NC = kBulkConsumers;
-    constexpr int TV = kBulkTileVecs;
+    constexpr int NW = kBulkWarps;
+    constexpr int TW = kBulkTileVecs;
     constexpr int J = kBulkJ;
-    constexpr int S = kBulkStages;
+    constexpr int R = kBulkStages;
     const ChunkParams &p = bp.c;
-    extern __shared__ __align__(128) unsigned char s_dyn[];
-    __shared__ __align__(8) uint64_t s_full[S], s_empty[S];
-    __shared__ int s_hist[256];
-    __shared__ int s_int[8 + 64];
-    __shared__ float s_red[NC / 32];
-    __shared__ int s_tmp[2], s_pick[4], s_count, s_flag[4];
-    __shared__ int s_nrec, s_novf, s_ncand;
-    __shared__ uint32_t s_tkey, s_epoch;
-    __shared__ int s_abort;
-
-    uint4 *const s_tiles = reinterpret_cast<uint4 *>(s_dyn);
-    uint64_t *const s_ra = reinterpret_cast<uint64_t *>(s_dyn + static_cast<size_t>(S) * TV * 16);
-    uint64_t *const s_rb = s_ra + kBulkRegion;
-    uint32_t *const s_rec = reinterpret_cast<uint32_t *>(s_rb + kBulkRegion);
-    uint32_t *const s_ovf = s_rec + (kBulkSlots + 1) * NC;
-    volatile uint32_t *const s_keys = s_ovf + kBulkOverflow;
+    uint4 *const s_tiles = reinterpret_cast<uint4 *>(s_bulk);
+    uint4 *const s_pool = reinterpret_cast<uint4 *>(s_bulk + kOffPool);
+    uint32_t *const s_pool_v = reinterpret_cast<uint32_t *>(s_bulk + kOffPoolV);
+    BulkCtl *const ctl = reinterpret_cast<BulkCtl *>(s_bulk + kOffCtl);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t grid = gridDim.x;
     const uint32_t nvv = static_cast<uint32_t>(p.nvv);
     const uint32_t total = static_cast<uint32_t>(p.rows) * nvv;
-    const uint32_t per = static_cast<uint32_t>(p.per_cta);
-    const uint32_t Vs = stream_boundary(blockIdx.x, grid, per, nvv, total, 0u);
-    const uint32_t Ve = stream_boundary(blockIdx.x + 1, grid, per, nvv, total, 0u);
+    const uint32_t P = static_cast<uint32_t>(p.parts_per_row);
+    const uint32_t Vs = stream_boundary(blockIdx.x, grid, 0u, nvv, total, P);
+    const uint32_t Ve = stream_boundary(blockIdx.x + 1, grid, 0u, nvv, total, P);
+    const int row = static_cast<int>(blockIdx.x / P);
+    const int part_v0 = static_cast<int>(Vs - static_cast<uint32_t>(row) * nvv);
+    const int part_len = static_cast<int>(Ve - Vs);  // (the planner leaves no part empty)
+    const int part_v1 = part_v0 + part_len;
+    const int ntiles = (part_len + TW - 1) / TW;
 
-    if (tid == 0) {
-        for (int s = 0; s < S; s++) {
-            mbar_init(smem_addr(&s_full[s]), 1u);
-            mbar_init(smem_addr(&s_empty[s]), NC / 32);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        s_nrec = 0;
-        s_novf = 0;
-        s_ncand = 0;
-        s_tkey = 0;
-        s_abort = 0;
-        s_flag[2] = 0;
+    if (tid < R) {
+        mbar_init(smem_addr(&ctl->full[tid]), 1u);
+        mbar_init(smem_addr(&ctl->empty[tid]), NW);
     }
-    if (tid < NC)
-        s_keys[tid] = 0u;
+    if (tid < NW)
+        ctl->wr[tid] = 0u;
+    if (tid == 0) {
+        ctl->nrec = 0;
+        ctl->nan_seen = 0;
+        ctl->tkey = 0;
+        ctl->abort = 0;
+        ctl->epoch_ready = 0;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     bool waited = false;
     if (!p.input_ready) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         waited = true;
     }
-    // The place of this call among the calls on its workspace: every CTA reads the call counter and
-    // then draws an arrival ticket; the CTA that draws the last ticket of the call advances the
-    // counter.  The next call is let in only after every CTA of this one has done so (the barrier
-    // below orders the draw before the signal), so all CTAs of a call read the same number.
-    if (tid == 0) {
-        unsigned int e, t;
-        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(p.epoch_word) : "memory");
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(p.arrive_word) : "memory");
-        if (t == grid - 1u) {
-            *p.arrive_word = 0u;
-            const unsigned int n = e + 1u;
-            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(n) : "memory");
-        }
-        s_epoch = e;
-    }
     __syncthreads();
-    const uint32_t epoch = s_epoch;
-    if (bp.trigger_tile <= 0 || Ve <= Vs)
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next call of the stream may start
-    if (Ve <= Vs)
-        return;
+    // The next kernel of the stream is let in when EVERY thread of every CTA has said so (or has
+    // exited): all threads say so now, except the one that numbers the call, which does it after that.
+    if (!(warp == NW + 1 && lane == 0))
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == NC / 32) {
-        // ================= producer: one thread feeds the ring =================
+    if (warp == NW) {
+        // ================= producer warp =================
+        // One thread hands the tiles of the part to the copy engine, one bulk copy each, at most R in the ring.
         if (lane == 0) {
-            TileWalk w;
-            w.start(Vs, Ve, nvv);
-            const char *base = static_cast<const char *>(p.logits);
+            const char *src0 = static_cast<const char *>(p.logits) + (static_cast<int64_t>(row) * p.vstride + part_v0) * 16;
             int t = 0;
-            bool triggered = bp.trigger_tile <= 0;
-            for (;;) {
-                const int stage = t % S;
-                if (t >= S && !mbar_wait(smem_addr(&s_empty[stage]), static_cast<uint32_t>((t / S - 1) & 1), &s_abort))
+            for (; t < ntiles; t++) {
+                const int stage = t % R;
+                if (t >= R && !mbar_wait(smem_addr(&ctl->empty[stage]), static_cast<uint32_t>((t / R - 1) & 1), &ctl->abort))
                     break;
-                const uint32_t bytes = static_cast<uint32_t>(w.nv) * 16u;
-                const char *src = base + (static_cast<int64_t>(w.row) * p.vstride + w.v0) * 16;
-                const uint32_t bar = smem_addr(&s_full[stage]);
+                const int nv = part_len - t * TW < TW ? part_len - t * TW : TW;
+                const uint32_t bytes = static_cast<uint32_t>(nv) * 16u, bar = smem_addr(&ctl->full[stage]);
                 mbar_expect_tx(bar, bytes);
-                bulk_copy_g2s(smem_addr(s_tiles + stage * TV), src, bytes, bar);
-                if (t == bp.trigger_tile && !triggered) {
-                    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-                    triggered = true;
-                }
-                t++;
-                if (!w.next())
-                    break;
+                bulk_copy_g2s(smem_addr(s_tiles + stage * TW), src0 + static_cast<int64_t>(t) * TW * 16, bytes, bar);
             }
-            if (!triggered)
-                asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            if (s_abort) {
+            if (ctl->abort) {
                 // copies in flight must land before the CTA's shared memory is given up
                 if (bp.status)
                     *bp.status = VKOP_TIMEOUT;
-                for (int u = (t > S ? t - S : 0); u < t; u++) {
+                for (int u = (t > R ? t - R : 0); u < t; u++) {
                     volatile int ignore = 0;
-                    mbar_wait(smem_addr(&s_full[u % S]), static_cast<uint32_t>((u / S) & 1), &ignore);
+                    mbar_wait(smem_addr(&ctl->full[u % R]), static_cast<uint32_t>((u / R) & 1), &ignore);
                 }
             }
         }
         return;
     }
+    if (warp == NW + 1) {
+        // ================= control warp =================
+        // One thread finds the place of this call among the calls on its workspace (needed at the end
+        // of the part): it reads the call counter and then draws an arrival ticket; the CTA that draws
+        // the last ticket of the call advances the counter.  Only then does the CTA let the next
+        // kernel of the stream in, so all CTAs of a call read the same number.
+        if (lane == 0) {
+            unsigned int e, tk;
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(p.epoch_word) : "memory");
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(tk) : "l"(p.arrive_word) : "memory");
+            if (tk == grid - 1u) {
+                *p.arrive_word = 0u;
+                const unsigned int nx = e + 1u;
+                asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(nx) : "memory");
+            }
+            ctl->epoch = e;
+            __threadfence_block();
+            *const_cast<volatile int *>(&ctl->epoch_ready) = 1;
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
+        return;
+    }
 
-    // ================= consumers =================
+    // ================= consumer warps =================
     const float c1 = p.inv_t * kLog2e;
     const int cols = static_cast<int>(p.cols);
     const bool ragged = cols % EPV != 0;
     const uint32_t xmask = p.negate ? (sizeof(T) == 4 ? 0x80000000u : 0x80008000u) : 0u;
-    uint32_t *const my_rec = s_rec + tid;
-    TileWalk w;
-    w.start(Vs, Ve, nvv);
-    int t = 0, pt = 0;
+    const int need_sum = p.need_sum;
+    const int rth = (p.k + NW - 1) / NW;  // NW times the rth-largest maximum of a warp: at least k maxima reach the smallest
+    const uint4 *const ring = s_tiles + tid;
     float m_t = -INFINITY, o_t = 0.0f;
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-    int cnt = 0;
-    bool nan_seen = false;
+    int nan_seen = 0;
     uint32_t tk_seen = 0u;
     float T_f = -INFINITY;
-    int part_v0 = w.v0;
-    for (;;) {
-        const int stage = t % S;
-        if (!mbar_wait(smem_addr(&s_full[stage]), static_cast<uint32_t>((t / S) & 1), &s_abort))
-            break;
+    bool alive = true;
+    for (int c = 0, lt = 0;; c++, lt++) {
+        const bool have = c < ntiles;
         uint4 d[J];
-        {
-            const uint4 *src = s_tiles + stage * TV + tid;
+        float a[J];
+        float vm = -INFINITY;
+        const int tv0 = part_v0 + c * TW;  // first vector of the tile in the row
+        if (have) {
+            const int stage = c % R;
+            // (a wait that runs out sets the abort flag; the warp then walks on without data, so that it
+            // still meets the others at every barrier, and the call reports VKOP_TIMEOUT)
+            alive = alive && mbar_wait(smem_addr(&ctl->full[stage]), static_cast<uint32_t>((c / R) & 1), &ctl->abort);
+            {
+                const uint4 *src = ring + stage * TW;
 #pragma unroll
-            for (int j = 0; j < J; j++)
-                d[j] = src[j * NC];
-        }
-        __syncwarp();
-        if (lane == 0)
-            mbar_arrive(smem_addr(&s_empty[stage]));
-        if (xmask) {  // "smallest": the sign bits are flipped and the largest are selected
-#pragma unroll
-            for (int j = 0; j < J; j++) {
-                d[j].x ^= xmask; d[j].y ^= xmask; d[j].z ^= xmask; d[j].w ^= xmask;
+                for (int j = 0; j < J; j++)
+                    d[j] = src[j * NC];
             }
-        }
-        const bool row_end = w.v0 + w.nv == static_cast<int>(nvv);
-        if (w.nv != TV || (ragged && row_end)) {
-            // a short tile, or the vector that holds the ragged end of the row: what is not data becomes -inf
-#pragma unroll
-            for (int j = 0; j < J; j++) {
-                const int lv = j * NC + tid;
-                if (lv >= w.nv) {
-                    const uint32_t f = Elem<T>::kNegInfWord;
-                    d[j] = make_uint4(f, f, f, f);
-                } else if (ragged && w.v0 + lv == static_cast<int>(nvv) - 1) {
-                    mask_vector<T>(d[j], 0, cols - (static_cast<int>(nvv) - 1) * EPV);
-                }
-            }
-        }
-        // ---- maximum of the thread's elements of this tile ----
-        float vm;
-        {
-            float a[J];
-#pragma unroll
-            for (int j = 0; j < J; j++)
-                a[j] = Elem<T>::vector_max(d[j]);
-            vm = a[0];
-#pragma unroll
-            for (int j = 1; j < J; j++)
-                vm = fmaxf(vm, a[j]);
-        }
-        if (vm > m_t) {
-            // the thread's maximum rises: new offset, the sum so far is rescaled
-            const float o_new = -__fmul_rn(vm, c1);
-            const float s = (s0 + s1) + (s2 + s3);
-            s0 = (m_t == -INFINITY && s == s) ? 0.0f : s * ex2_approx(o_new - o_t);
-            s1 = s2 = s3 = 0.0f;
-            m_t = vm;
-            o_t = o_new;
-            s_keys[tid] = order_key(vm);
-        }
-        if (p.need_sum && !(bp.debug & 4)) {
-#pragma unroll
-            for (int j = 0; j < J; j++) {
-                float f[EPV];
-                Elem<T>::unpack(d[j], f);
-#pragma unroll
-                for (int q = 0; q < EPV; q += 4) {
-                    s0 += ex2_approx(__fmaf_rn(f[q], c1, o_t));
-                    s1 += ex2_approx(__fmaf_rn(f[q + 1], c1, o_t));
-                    s2 += ex2_approx(__fmaf_rn(f[q + 2], c1, o_t));
-                    s3 += ex2_approx(__fmaf_rn(f[q + 3], c1, o_t));
-                }
-            }
-        } else {
-            // no sum to carry a NaN: look for it (fmaxf passes NaN over)
-#pragma unroll
-            for (int j = 0; j < J; j++)
-                nan_seen |= Elem<T>::vector_has_nan(d[j]);
-        }
-
-        // ---- the bound ----
-        if (bp.debug & 8) {
-        } else if (w.part_first) {
-            // first tile of a part: everybody waits for the first bound
-            cta_sync<kBar, NC>();
-            if (warp == 0) {
-                const uint32_t tk = bulk_bisect(s_keys, p.k, 0u, 24);
-                if (lane == 0)
-                    s_tkey = tk;
-            }
-            cta_sync<kBar, NC>();
-        } else if ((pt & (pt + 1)) == 0 && warp == ((31 - __clz(pt + 1)) & (NC / 32 - 1))) {
-            // tiles 1, 3, 7, ...: one warp in turn tightens the bound while the others stream on
-            const uint32_t tk = bulk_bisect(s_keys, p.k, *reinterpret_cast<volatile uint32_t *>(&s_tkey), 20);
+            __syncwarp();
             if (lane == 0)
-                atomicMax(&s_tkey, tk);
+                mbar_arrive(smem_addr(&ctl->empty[stage]));
+            if (!alive) {  // (no data came: the tile counts as padding)
+                const uint32_t f = Elem<T>::kNegInfWord;
+#pragma unroll
+                for (int j = 0; j < J; j++)
+                    d[j] = make_uint4(f, f, f, f);
+            }
+            if (xmask) {  // "smallest": the sign bits are flipped and the largest are selected
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    d[j].x ^= xmask; d[j].y ^= xmask; d[j].z ^= xmask; d[j].w ^= xmask;
+                }
+            }
+            const int nv = part_v1 - tv0 < TW ? part_v1 - tv0 : TW;
+            if (nv != TW || (ragged && tv0 + nv == static_cast<int>(nvv))) {
+                // a short tile, or the vector that holds the ragged end of the row: what is not data becomes -inf
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    const int lv = j * NC + tid;
+                    if (lv >= nv) {
+                        const uint32_t f = Elem<T>::kNegInfWord;
+                        d[j] = make_uint4(f, f, f, f);
+                    } else if (ragged && tv0 + lv == static_cast<int>(nvv) - 1) {
+                        mask_vector<T>(d[j], 0, cols - (static_cast<int>(nvv) - 1) * EPV);
+                    }
+                }
+            }
+            // ---- maxima of the lane's vectors ----
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                a[j] = Elem<T>::vector_max(d[j]);
+                vm = fmaxf(vm, a[j]);
+            }
+            if (vm > m_t) {
+                // the thread's maximum rises: new offset, the sum so far is rescaled
+                const float o_new = -__fmul_rn(vm, c1);
+                const float s = (s0 + s1) + (s2 + s3);
+                s0 = (m_t == -INFINITY && s == s) ? 0.0f : s * ex2_approx(o_new - o_t);
+                s1 = s2 = s3 = 0.0f;
+                m_t = vm;
+                o_t = o_new;
+            }
+            if (need_sum) {
+#pragma unroll
+                for (int j = 0; j < J; j++) {
+                    float f[EPV];
+                    Elem<T>::unpack(d[j], f);
+#pragma unroll
+                    for (int q = 0; q < EPV; q += 4) {
+                        s0 += ex2_approx(__fmaf_rn(f[q], c1, o_t));
+                        s1 += ex2_approx(__fmaf_rn(f[q + 1], c1, o_t));
+                        s2 += ex2_approx(__fmaf_rn(f[q + 2], c1, o_t));
+                        s3 += ex2_approx(__fmaf_rn(f[q + 3], c1, o_t));
+                    }
+                }
+            } else {
+                // no sum to carry a NaN: look for it (fmaxf passes NaN over)
+#pragma unroll
+                for (int j = 0; j < J; j++)
+                    nan_seen |= Elem<T>::vector_has_nan(d[j]) ? 1 : 0;
+            }
         }
+        // ---- the bound: after its tiles 0, 1, 3, 7, ... of the part the warp posts the rth largest of
+        // its running thread maxima; the smallest posted key is reached by at least k maxima ----
+        if ((lt & (lt + 1)) == 0 && (have || lt == 0)) {
+            const uint32_t wr = have ? warp_rth_largest(m_t == -INFINITY ? 0u : order_key(m_t), rth) : 0u;
+            if (lane == 0)
+                *const_cast<volatile uint32_t *>(&ctl->wr[warp]) = wr;
+            if (lt == 0) {
+                // first tile of the part: everybody waits for the first bound (a warp without a tile
+                // posts "none", which leaves a tiny part without a bound)
+                cta_sync<kBar, NC>();
+                const uint32_t t0 = posted_bound<NW>(ctl->wr);
+                if (t0 != 0u) {
+                    tk_seen = t0;
+                    T_f = key_to_float(t0);
+                    if (tid == 0)
+                        atomicMax(&ctl->tkey, t0);
+                }
+            } else {
+                // later: no barrier; whoever posts takes the minimum of what is posted (keys only grow)
+                __syncwarp();
+                const uint32_t tn = posted_bound<NW>(ctl->wr);
+                if (lane == 0 && tn > tk_seen)
+                    atomicMax(&ctl->tkey, tn);
+            }
+        }
+        if (!have)
+            break;
         {
-            const uint32_t tk = *reinterpret_cast<volatile uint32_t *>(&s_tkey);
-            if (tk != tk_seen) {
+            const uint32_t tk = *reinterpret_cast<volatile uint32_t *>(&ctl->tkey);
+            if (tk > tk_seen) {
                 tk_seen = tk;
                 T_f = key_to_float(tk);
             }
         }
-        // ---- a group that reaches the bound is recorded (where it is, not what it holds) ----
-        {
-            const bool hit = (bp.debug & 2) ? false : vm >= T_f;
-            const int slot = cnt < kBulkSlots ? cnt : kBulkSlots;
-            if (hit)
-                my_rec[slot * NC] = static_cast<uint32_t>(w.v0 + tid);
-            if (hit && cnt >= kBulkSlots) {
-                const int pos = atomicAdd(&s_novf, 1);
-                if (pos < kBulkOverflow)
-                    s_ovf[pos] = static_cast<uint32_t>(w.v0 + tid);
-            }
-            cnt += hit ? 1 : 0;
-        }
-
-        const bool part_last = w.part_last;
-        const int c_row = w.row, c_v1 = w.v0 + w.nv;
-        const bool more = w.next();
-        t++;
-        pt++;
-        if (part_last) {
-            BulkPartEnd e;
-            e.m_t = m_t;
-            e.o_t = o_t;
-            e.s_t = (s0 + s1) + (s2 + s3);
-            e.cnt = cnt;
-            e.nan_seen = nan_seen;
-            e.row = c_row;
-            e.part_v0 = part_v0;
-            e.part_v1 = c_v1;
-            e.epoch = epoch;
-            e.waited = waited;
-            BulkShared sh;
-            sh.tiles = s_tiles;
-            sh.ra = s_ra;
-            sh.rb = s_rb;
-            sh.rec = s_rec;
-            sh.ovf = s_ovf;
-            sh.keys = s_keys;
-            sh.hist = s_hist;
-            sh.sint = s_int;
-            sh.tmp = s_tmp;
-            sh.pick = s_pick;
-            sh.count = &s_count;
-            sh.flag = s_flag;
-            sh.red = s_red;
-            sh.nrec = &s_nrec;
-            sh.novf = &s_novf;
-            sh.ncand = &s_ncand;
-            sh.tkey = &s_tkey;
-            sh.abort = &s_abort;
-            if (!(bp.debug & 1))
-                waited = bulk_finish_part<T>(bp, sh, e);
-            if (more) {
-                // ---- reset for the next row part ----
-                cta_sync<kBar, NC>();  // everybody is done with the regions, the keys and the counters
-                s_keys[tid] = 0u;
-                if (tid == 0) {
-                    s_nrec = 0;
-                    s_novf = 0;
-                    s_ncand = 0;
-                    s_tkey = 0;
-                    s_flag[2] = 0;
+        // ---- a vector that reaches the bound goes to the pool as it is, with its place in the row ----
+        if (vm >= T_f) {
+            int cnt = 0;
+#pragma unroll
+            for (int j = 0; j < J; j++)
+                cnt += (a[j] >= T_f && tv0 + j * NC + tid < part_v1) ? 1 : 0;
+            int pos = atomicAdd(&ctl->nrec, cnt);
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int v = tv0 + j * NC + tid;
+                if (a[j] >= T_f && v < part_v1) {
+                    if (pos < kBulkPool) {
+                        s_pool[pos] = d[j];
+                        s_pool_v[pos] = static_cast<uint32_t>(v);
+                    }
+                    pos++;
                 }
-                m_t = -INFINITY;
-                o_t = 0.0f;
-                s0 = s1 = s2 = s3 = 0.0f;
-                cnt = 0;
-                nan_seen = false;
-                tk_seen = 0u;
-                T_f = -INFINITY;
-                part_v0 = w.v0;
-                pt = 0;
-                cta_sync<kBar, NC>();
             }
         }
-        if (!more)
-            break;
     }
-    if (s_abort && tid == 0 && bp.status)
+
+    // ================= end of the part: statistics and the pool go to scratch memory =================
+    {
+        const uint32_t key = m_t == -INFINITY ? 0u : order_key(m_t);
+        const uint32_t wm = __reduce_max_sync(kFullMask, key);
+        if (lane == 0)
+            ctl->wm[warp] = wm;
+        if (nan_seen)
+            ctl->nan_seen = 1;
+    }
+    if (tid == 0) {
+        // the call number was drawn by the control warp microseconds ago; bounded all the same
+        const volatile int *ready = &ctl->epoch_ready;
+        for (int i = 0; i < (1 << 22) && !*ready; i++)
+            __nanosleep(32);
+        if (!*ready)
+            ctl->abort = 1;
+        // This set of pools last served the call kBulkSets calls ago: has the selection of that call
+        // read this row's pools?  (It has, unless the selections are many calls behind.)
+        const uint32_t e = ctl->epoch;
+        if (!waited && !ctl->abort && !wait_row_counter(p.row_done + row, e + 1u - kBulkSets, false))
+            ctl->abort = 1;
+    }
+    cta_sync<kBar, NC>();  // maxima, pool, bound and call number are final; the scratch set is free
+    const uint32_t epoch = ctl->epoch;
+    unsigned char *const part = bp.scratch + (static_cast<size_t>(epoch % kBulkSets) * grid + blockIdx.x) * kPartStride;
+    uint32_t mkey = 0;
+#pragma unroll
+    for (int q = 0; q < NW; q++)
+        mkey = ctl->wm[q] > mkey ? ctl->wm[q] : mkey;
+    const float M = mkey ? key_to_float(mkey) : -INFINITY;  // part maximum of the stored logits
+    const float O = -__fmul_rn(M, c1);
+    {
+        const float s_t = (s0 + s1) + (s2 + s3);
+        const float contrib = (m_t == -INFINITY && s_t == s_t) ? 0.0f : s_t * ex2_approx(O - o_t);
+        const float ws = warp_sum(contrib);
+        if (lane == 0)
+            ctl->red[warp] = ws;
+    }
+    const int n_rec = ctl->nrec;
+    const bool pool_bad = ctl->nan_seen != 0 || n_rec > kBulkPool || ctl->abort != 0;
+    if (!pool_bad) {
+        uint4 *const gpool = reinterpret_cast<uint4 *>(part + sizeof(PartHeader));
+        uint32_t *const gpos = reinterpret_cast<uint32_t *>(part + sizeof(PartHeader) + static_cast<size_t>(kBulkPool) * 16);
+        for (int i = tid; i < n_rec; i += NC) {
+            gpool[i] = s_pool[i];
+            gpos[i] = s_pool_v[i];
+        }
+    }
+    cta_sync<kBar, NC>();
+    if (tid == 0) {
+        float S = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; w++)
+            S += ctl->red[w];
+        // S is relative to the offset O = -rn(M * c1); the published sum is relative to M exactly
+        if (M != -INFINITY)
+            S *= ex2_approx(-__fmaf_rn(M, c1, O));
+        PartHeader h;
+        h.mz = __fmul_rn(M, p.inv_t);
+        h.sum = S;
+        h.tkey = ctl->tkey;
+        h.count = (pool_bad || (need_sum && S != S)) ? -1 : n_rec;
+        h.epoch = epoch;
+        h.pad[0] = h.pad[1] = h.pad[2] = 0u;
+        *reinterpret_cast<uint4 *>(part) = *reinterpret_cast<const uint4 *>(&h);
+        *reinterpret_cast<uint4 *>(part + 16) = *(reinterpret_cast<const uint4 *>(&h) + 1);
+        if (ctl->abort && bp.status)
+            *bp.status = VKOP_TIMEOUT;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Kernel 2: one CTA per row gathers what the parts of the row left, selects and writes the result.
+
+// Ranks n distinct candidates held in shared memory by counting (the rank of a candidate is the
+// number of candidates that beat it) and emits those of rank < k at their rank.  PER threads share
+// one candidate's count.  No barrier; buf is only read.
+template <typename T>
+__device__ __forceinline__ void rank_emit(const ChunkParams &p, int64_t row, const uint64_t *buf, int n, float M, float S) {
+    constexpr int NT = kSelThreads;
+    const int tid = threadIdx.x;
+    int per = 1;
+    while (per < 8 && n * per * 2 <= NT)
+        per *= 2;
+    const int sub = tid & (per - 1);
+    for (int c0 = 0; c0 < n; c0 += NT / per) {
+        const int c = c0 + tid / per;
+        const uint64_t me = c < n ? buf[c] : ~0ull;
+        // (independent counts, several loads in flight: a plain loop would pay the shared-memory
+        // latency once per candidate)
+        int b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+        int i = sub;
+        for (; i + 7 * per < n; i += 8 * per) {
+            uint64_t x[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                x[u] = buf[i + u * per];
+            b0 += (x[0] > me ? 1 : 0) + (x[4] > me ? 1 : 0);
+            b1 += (x[1] > me ? 1 : 0) + (x[5] > me ? 1 : 0);
+            b2 += (x[2] > me ? 1 : 0) + (x[6] > me ? 1 : 0);
+            b3 += (x[3] > me ? 1 : 0) + (x[7] > me ? 1 : 0);
+        }
+        for (; i < n; i += per)
+            b0 += buf[i] > me ? 1 : 0;
+        int beat = (b0 + b1) + (b2 + b3);
+        for (int o = 1; o < per; o <<= 1)
+            beat += __shfl_xor_sync(kFullMask, beat, o);
+        if (c < n && sub == 0 && beat < p.k)
+            emit<T>(p, row, beat, me, M, S, nullptr);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSelThreads) bulk_select_kernel(const __grid_constant__ BulkParams bp) {
+    constexpr int EPV = Elem<T>::kPerVec;
+    constexpr int NT = kSelThreads;
+    constexpr int NW = NT / 32;
+    const ChunkParams &p = bp.c;
+    __shared__ __align__(16) uint64_t s_a[kSelCap], s_b[kCandCap];  // candidates; tightened candidates / exact fallback
+    __shared__ PartHeader s_hdr[kBulkMaxParts];
+    __shared__ uint32_t s_wr[NW];
+    __shared__ int s_hist[256], s_pick[4], s_count, s_n[2];
+    __shared__ uint32_t s_epoch;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x;
+    const int P = p.parts_per_row;
+    const int cols = static_cast<int>(p.cols);
+    const uint32_t nvv = static_cast<uint32_t>(p.nvv);
+    const uint32_t nparts = static_cast<uint32_t>(p.rows) * static_cast<uint32_t>(P);
+    // (the next kernel of the stream is let in when every thread of every CTA has said so: all do at
+    // once, except the one that numbers the call, which does it after that)
+    if (tid != 0)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        s_n[0] = 0;
+        s_n[1] = 0;
+        // The place of this call among the calls on its workspace, found as the streaming kernel finds
+        // its own (the two counts run in step): call counter, then an arrival ticket; the last CTA of
+        // the call to arrive advances the counter.  Only then is the next kernel of the stream let in.
+        unsigned int e, tk;
+        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(bp.epoch2) : "memory");
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(tk) : "l"(bp.arrive2) : "memory");
+        if (tk == gridDim.x - 1u) {
+            *bp.arrive2 = 0u;
+            const unsigned int nx = e + 1u;
+            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(bp.epoch2), "r"(nx) : "memory");
+        }
+        s_epoch = e;
+        // the next call's streaming kernel may start: this kernel is small and runs beside it
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    // everything the streaming kernel of this call wrote is visible after this
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const unsigned char *const set = bp.scratch + static_cast<size_t>(epoch % kBulkSets) * nparts * kPartStride;
+    if (tid < P)
+        s_hdr[tid] = *reinterpret_cast<const PartHeader *>(set + (static_cast<size_t>(row) * P + tid) * kPartStride);
+    __syncthreads();
+    uint32_t trow = 0;
+    float M = -INFINITY;
+    bool any_bad = false;
+    int total = 0;
+    for (int j = 0; j < P; j++) {
+        trow = s_hdr[j].tkey > trow ? s_hdr[j].tkey : trow;
+        M = fmaxf(M, s_hdr[j].mz);
+        any_bad |= s_hdr[j].count < 0;
+        total += s_hdr[j].count > 0 ? s_hdr[j].count : 0;
+    }
+    float S = 0.0f;
+    for (int j = 0; j < P; j++) {
+        const float sj = s_hdr[j].sum;
+        if (sj != 0.0f)  // an all -inf part has sum 0 and no defined maximum
+            S += sj * expf(s_hdr[j].mz - M);
+    }
+    // A part whose pool is no use (NaN, massive ties) makes its bound no use either.
+    if (any_bad)
+        trow = 0;
+    const float Tf = trow ? key_to_float(trow) : -INFINITY;
+
+    // ---- the pooled vectors of all parts: the elements that reach the row's bound become candidates ----
+    for (int f0 = 0; f0 < total; f0 += 4 * NT) {
+        // four pooled vectors in flight per thread: one round trip to L2 for the usual row
+        uint4 dd[4];
+        int vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int f = f0 + u * NT + tid;
+            vv[u] = -1;
+            if (f < total) {
+                int j = 0, i = f;
+                while (i >= (s_hdr[j].count > 0 ? s_hdr[j].count : 0)) {
+                    i -= s_hdr[j].count > 0 ? s_hdr[j].count : 0;
+                    j++;
+                }
+                const unsigned char *part = set + (static_cast<size_t>(row) * P + j) * kPartStride;
+                dd[u] = __ldcg(reinterpret_cast<const uint4 *>(part + sizeof(PartHeader)) + i);
+                vv[u] = static_cast<int>(__ldcg(reinterpret_cast<const uint32_t *>(part + sizeof(PartHeader) + static_cast<size_t>(kBulkPool) * 16) + i));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float x[EPV];
+            Elem<T>::unpack(dd[u], x);
+            const int v = vv[u];
+            unsigned mine = 0;
+            if (v >= 0) {
+#pragma unroll
+                for (int q = 0; q < EPV; q++)
+                    mine |= (v * EPV + q < cols && x[q] >= Tf) ? 1u << q : 0u;
+            }
+            const int cnt = __popc(mine);
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(kFullMask, incl, o);
+                if (lane >= o)
+                    incl += y;
+            }
+            const int wtotal = __shfl_sync(kFullMask, incl, 31);
+            if (wtotal == 0)
+                continue;
+            int base = 0;
+            if (lane == 31)
+                base = atomicAdd(&s_n[0], wtotal);
+            int pos = __shfl_sync(kFullMask, base, 31) + incl - cnt;
+#pragma unroll
+            for (int q = 0; q < EPV; q++) {
+                if (mine & (1u << q)) {
+                    if (pos < kSelCap)
+                        s_a[pos] = make_cand(order_key(x[q]), static_cast<uint32_t>(v * EPV + q));
+                    pos++;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    int n = s_n[0];
+    const uint64_t *best = s_a;
+    if (any_bad || n > kSelCap) {
+        // Rare: exact radix select over the whole row, re-read from L2 (the pooled vectors were sign-
+        // flipped where the smallest are wanted; the fallback flips for itself).
+        const uint4 *vbase = reinterpret_cast<const uint4 *>(p.logits) + static_cast<int64_t>(row) * p.vstride;
+        const int kk = cols < p.k ? cols : p.k;
+        select_fallback<T, NT>(vbase, 0, static_cast<int64_t>(nvv), 0, p.cols, p.negate, kk, s_b, &s_count, s_hist, s_pick);
+        n = s_count;
+        best = s_b;
+    } else if (n > 2 * p.k && n > 96) {
+        // Many candidates for a ranking by counting: a closer bound first.  Every thread takes the
+        // largest key of its share of the candidates, every warp the rth largest of those (NW * rth >=
+        // k); at least k candidates reach the smallest of the warps' values.
+        uint32_t key = 0;
+        for (int c = tid; c < n; c += NT) {
+            const uint32_t kc = cand_key(s_a[c]);
+            key = kc > key ? kc : key;
+        }
+        const uint32_t wr = warp_rth_largest(key, (p.k + NW - 1) / NW);
+        if (lane == 0)
+            s_wr[warp] = wr;
+        __syncthreads();
+        const uint32_t bound = posted_bound<NW>(s_wr);
+        for (int c0 = 0; c0 < n; c0 += NT) {
+            const int c = c0 + tid;
+            const uint64_t cd = c < n ? s_a[c] : 0ull;
+            const bool pass = c < n && cand_key(cd) >= bound;
+            const unsigned bal = __ballot_sync(kFullMask, pass);
+            if (bal != 0u) {
+                int base = 0;
+                if (lane == 0)
+                    base = atomicAdd(&s_n[1], __popc(bal));
+                base = __shfl_sync(kFullMask, base, 0);
+                if (pass)
+                    s_b[base + __popc(bal & ((1u << lane) - 1u))] = cd;
+            }
+        }
+        __syncthreads();
+        n = s_n[1];
+        best = s_b;
+    }
+    if (p.packets_out && tid == 0) {
+        uint32_t *pk = p.packets_out + static_cast<int64_t>(row) * packet_words(p.k);
+        pk[0] = __float_as_uint(M);
+        pk[1] = __float_as_uint(S);
+        pk[2] = static_cast<uint32_t>(n < p.k ? n : p.k);
+        pk[3] = 0;
+    }
+    // results of one row are written in call order (the previous call's selection is rarely behind)
+    if (tid == 0 && !wait_row_counter(p.row_done + row, epoch, true) && bp.status)
         *bp.status = VKOP_TIMEOUT;
+    __syncthreads();
+    rank_emit<T>(p, row, best, n, M, S);
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int d = epoch + 1u;
+        asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.row_done + row), "r"(d) : "memory");
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -764,7 +783,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) softmax_topk_bulk_kernel(cons
 size_t stream_common_bytes(int64_t rows) { return 256 + ((static_cast<size_t>(rows) * 4 + 255) / 256) * 256; }
 
 int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan) {
-    if (d.k > kChunkMaxK || d.splits > 0)
+    if (d.k > kChunkMaxK)
         return VKOP_UNSUPPORTED;
     const int esz = d.dtype == VKOP_F32 ? 4 : 2;
     const int epv = 16 / esz;
@@ -772,55 +791,44 @@ int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan
     if (!base_aligned || (stride * esz) % 16 != 0)
         return VKOP_UNSUPPORTED;  // the bulk copies need 16-byte aligned rows
     const int64_t nvv = (d.cols + epv - 1) / epv;
-    if (d.rows <= 0 || d.rows >= (1ll << 31) || d.cols >= (1ll << 30) || d.rows * nvv >= (1ll << 32) - (1ll << 20))
+    if (d.rows <= 0 || d.rows >= (1ll << 28) || d.cols >= (1ll << 30) || d.rows * nvv >= (1ll << 32) - (1ll << 20))
         return VKOP_UNSUPPORTED;
-    if (nvv < 2 * kBulkTileVecs)
-        return VKOP_UNSUPPORTED;  // short rows: a row end per tile or two would dominate
-    const int64_t total = d.rows * nvv;
-    const int64_t tiles = (total + kBulkTileVecs - 1) / kBulkTileVecs;
+    if (nvv < kBulkMinPartVecs)
+        return VKOP_UNSUPPORTED;  // short rows: the end of a part every few tiles would dominate
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess)
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaGetLastError();
-    int64_t grid = sms < tiles ? sms : tiles;  // one CTA per SM; a second call may share the SM
-    const int64_t need = d.k > 64 ? d.k : 64;  // a part publishes at least its own k best
-    // parts a row can be cut into: its share of the CTAs, plus one at either end.  The CTA that merges
-    // a row gathers all its parts' lists in one work region: fewer CTAs when that would not fit.
-    int64_t per, maxparts;
-    for (;;) {
-        per = (total + grid - 1) / grid;
-        maxparts = (nvv + per - 1) / per + 2;
-        if ((maxparts <= kBulkMaxParts && maxparts * need <= kBulkRegion) || grid == 1)
-            break;
-        grid = grid * 7 / 8 > 0 ? grid * 7 / 8 : 1;
+    // Parts per row: the smallest power of two that fills most of the CTA slots of the GPU (two per
+    // SM) with one call, every part at least kBulkMinPartVecs vectors (the caller may name it in
+    // desc.splits).
+    int P = 1;
+    if (d.splits > 0) {
+        P = d.splits;
+        if (P > kBulkMaxParts || nvv / P < kBulkMinPartVecs)
+            return VKOP_UNSUPPORTED;
+    } else {
+        while (P < kBulkMaxParts && d.rows * P * 5 < static_cast<int64_t>(sms) * VKOP_BULK_CTAS_PER_SM * 4 &&
+               nvv / (2 * P) >= kBulkMinPartVecs)
+            P *= 2;
     }
-    if (maxparts > kBulkMaxParts || maxparts * need > kBulkRegion)
-        return VKOP_UNSUPPORTED;
-    int list_cap = static_cast<int>(kBulkRegion / maxparts);
-    if (list_cap > 256)
-        list_cap = 256;
-    plan->grid = static_cast<int>(grid);
-    plan->per_cta = per;
     plan->nvv = nvv;
     plan->vstride = stride * esz / 16;
-    plan->maxparts = static_cast<int>(maxparts);
-    plan->list_cap = list_cap;
-    plan->counters_bytes = ((static_cast<size_t>(d.rows) * 2 * 4 + 255) / 256) * 256;
-    plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
-    plan->smem_bytes = static_cast<size_t>(kBulkStages) * kBulkTileVecs * 16 + 2 * static_cast<size_t>(kBulkRegion) * 8 +
-                       (static_cast<size_t>(kBulkSlots + 1) * kBulkConsumers + kBulkOverflow + kBulkConsumers) * 4;
+    plan->smem_bytes = kBulkSmemBytes;
+    plan->parts = P;
+    plan->grid = static_cast<int>(d.rows * P);
+    plan->scratch_bytes = kBulkSets * static_cast<size_t>(d.rows) * P * kPartStride;
     return VKOP_OK;
 }
 
-template <typename T>
-static int launch_bulk_t(const BulkParams &bp, const BulkPlan &plan, cudaStream_t stream) {
-    auto kern = softmax_topk_bulk_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess)
+template <typename Kern>
+static int launch_pdl(Kern kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream, const BulkParams &bp) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return VKOP_CUDA_ERROR;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
-    cfg.blockDim = dim3(kBulkThreads);
-    cfg.dynamicSmemBytes = plan.smem_bytes;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -831,6 +839,14 @@ static int launch_bulk_t(const BulkParams &bp, const BulkPlan &plan, cudaStream_
         return VKOP_CUDA_ERROR;
     note_launch(1);
     return check_launch();
+}
+
+template <typename T>
+static int launch_bulk_t(const BulkParams &bp, const BulkPlan &plan, cudaStream_t stream) {
+    int rc = launch_pdl(bulk_stream_kernel<T>, static_cast<unsigned>(plan.grid), kBulkThreads, plan.smem_bytes, stream, bp);
+    if (rc != VKOP_OK)
+        return rc;
+    return launch_pdl(bulk_select_kernel<T>, static_cast<unsigned>(bp.c.rows), kSelThreads, 0, stream, bp);
 }
 
 int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const void *logits, void *out_values, void *out_indices,
@@ -846,9 +862,6 @@ int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const voi
     p.cols = d.cols;
     p.row_stride = d.row_stride ? d.row_stride : d.cols;
     p.k = d.k;
-    p.splits = plan.maxparts;
-    p.vps = 0;
-    p.list_cap = plan.list_cap;
     p.inv_t = d.inv_temperature;
     p.value_kind = d.value_kind;
     p.index_dtype = d.index_dtype;
@@ -859,19 +872,17 @@ int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const voi
     p.out_indices = out_indices;
     p.packets_out = reinterpret_cast<uint32_t *>(packets_out);
     p.nvv = plan.nvv;
-    p.per_cta = plan.per_cta;
     p.vstride = plan.vstride;
-    p.parts_per_row = 0;
+    p.parts_per_row = plan.parts;
     p.input_ready = (d.flags & VKOP_FLAG_INPUT_READY) ? 1 : 0;
     char *cw = static_cast<char *>(common_ws);
     p.arrive_word = reinterpret_cast<unsigned int *>(cw);
     p.epoch_word = reinterpret_cast<unsigned int *>(cw + 4);
     bp.status = reinterpret_cast<int *>(cw + 8);
+    bp.arrive2 = reinterpret_cast<unsigned int *>(cw + 12);
+    bp.epoch2 = reinterpret_cast<unsigned int *>(cw + 16);
     p.row_done = reinterpret_cast<unsigned int *>(cw + 256);
-    p.counters = reinterpret_cast<unsigned int *>(bulk_ws);
-    p.lists = reinterpret_cast<unsigned long long *>(static_cast<char *>(bulk_ws) + plan.counters_bytes);
-    bp.trigger_tile = getenv("VKOP_BULK_TRIGGER") ? atoi(getenv("VKOP_BULK_TRIGGER")) : 0;
-    bp.debug = getenv("VKOP_BULK_DEBUG") ? atoi(getenv("VKOP_BULK_DEBUG")) : 0;
+    bp.scratch = static_cast<unsigned char *>(bulk_ws);
     switch (d.dtype) {
     case VKOP_F32: return launch_bulk_t<float>(bp, plan, stream);
     case VKOP_F16: return launch_bulk_t<__half>(bp, plan, stream);
