@@ -16,13 +16,21 @@ over ranks is reported.  Consecutive steps read different input buffers (8
 buffers, 263 MB in total, more than the 126 MB L2), so every step streams its
 logits from HBM.
 
+The steps are captured once in a CUDA graph (K steps when K <= 256, else 256 that are replayed),
+the graph is replayed untimed as extra warm-up, and the timed region replays it: the launch-bound
+loop then costs no host time.  `--no-graph` launches every step from the host instead.
+
 The JSON line carries, besides the contract keys:
   roofline      algorithmic bytes per launch / mean launch duration, against the
                 measured HBM copy bandwidth of this pool
   e2e           same metric through host buffers: pinned host logits -> device,
                 the operator, results -> host, every step
-  cpu_baseline  the CPU oracle (a port of the reference's own CPU statement of
-                this path) timed on this machine's cores (rank 0, N = 1 only)
+  serialized    the same steps without VKOP_FLAG_INPUT_READY: every call waits for the one before
+  vocab_sharded the 512 x 256000 bf16, k = 64 configuration with the columns split over the N ranks
+                (partial selection per rank, packet exchange, merge); at N = 1 the whole matrix on one GPU
+  cpu_baseline  the reference's own CPU code for this path (core/function.cpp, compiled into oracle/_ref)
+                or, where that is not built, the oracle port of it, timed on this machine's cores
+                (rank 0, N = 1 only), with torch-CPU softmax + topk beside it
 """
 from __future__ import annotations
 
@@ -48,10 +56,26 @@ WORKLOADS = {
 }
 NBUF = 8
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the streaming kernel, from the ncu
-# capture summarised in profiles/softmax_topk_stream_llm_vocab_f32_full.md; None for workloads
-# without a capture.
-NCU_TRAFFIC_BYTES = {"llm_vocab_f32": 32997376}
+# ncu capture summaries that state the DRAM traffic of one launch of the workload's dominant kernel
+TRAFFIC_SUMMARY = {"llm_vocab_f32": "softmax_topk_stream_llm_vocab_f32_full.md"}
+
+
+def ncu_traffic_bytes(workload):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, read from the committed capture summary
+    (None for workloads without one)."""
+    import re
+
+    name = TRAFFIC_SUMMARY.get(workload)
+    path = os.path.join(ROOT, "profiles", name) if name else None
+    if not path or not os.path.exists(path):
+        return None
+    total = 0
+    with open(path) as f:
+        for line in f:
+            m = re.match(r"\|\s*`dram__bytes_(read|write)\.sum`\s*\|\s*([0-9 ]+)\s*B", line)
+            if m:
+                total += int(m.group(2).replace(" ", ""))
+    return total or None
 
 
 def algorithmic_bytes(rows, cols, dtype, k):
@@ -154,24 +178,38 @@ def make_inputs(name, seed_base, device):
     return bufs
 
 
+def cpu_reference_step(name):
+    """One CPU pass over one batch of the workload with every host thread.  Returns (step function, cores, kind,
+    what it runs): the reference's own Function::get_top_k_predictions compiled from its source (oracle/_ref;
+    fp32 only) when that library exists, else the oracle port of it."""
+    import oracle
+    from oracle import ref
+
+    rows, cols, dtype, k, inv_t = WORKLOADS[name]
+    x = make_inputs(name, 1000, "cpu")[0]
+    ncores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if dtype == torch.float32 and ref.available():
+        xa = x.numpy()
+        ref.set_num_threads(ncores)
+        return (lambda: ref.function_top_k_predictions(xa, k, inv_t)), ncores, "reference", \
+            "core/function.cpp Function::get_top_k_predictions (max, exp, sequential fp32 sum, divide, std::sort), " \
+            "compiled from the reference source, one call per row, OpenMP over rows"
+    xa = oracle.to_oracle_array(x)
+    # every host thread, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)
+    oracle.set_num_threads(ncores)
+    dt = oracle.oracle_dtype(dtype)
+    return (lambda: oracle.softmax_topk(xa, k, inv_t, dtype=dt, sum_mode=oracle.SUM_F32_SEQUENTIAL, full_sort=True)), \
+        oracle.num_threads(), "port", \
+        "oracle port of core/function.cpp:150-183 (max, exp, sequential fp32 sum, divide, full sort; qsort where the " \
+        "reference uses std::sort), OpenMP over rows"
+
+
 def run_reference(args, rank, world):
-    """The reference's CPU statement of the path (oracle port), all host threads, on the same workload."""
+    """The reference's CPU statement of the path, all host threads, on the same workload."""
     if rank != 0:
         return
-    import oracle
-    from tests.util import ORACLE_DTYPE, to_oracle_array
-    from vkop_b200 import workloads
-
     rows, cols, dtype, k, inv_t = WORKLOADS[args.workload]
-    x = make_inputs(args.workload, 1000, "cpu")[0]
-    xa = to_oracle_array(x)
-    # every host thread, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)
-    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
-    cores = oracle.num_threads()
-
-    def step():
-        oracle.softmax_topk(xa, k, inv_t, dtype=ORACLE_DTYPE[dtype], sum_mode=oracle.SUM_F32_SEQUENTIAL, full_sort=True)
-
+    step, cores, kind, what = cpu_reference_step(args.workload)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
@@ -184,10 +222,9 @@ def run_reference(args, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""),
         "data": "synthetic",
-        "config": {"workload": args.workload, "rows": rows, "cols": cols, "k": k, "inv_temperature": inv_t},
-        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": "port",
-                         "sample": f"one batch of {rows} rows per step; max -> exp -> sequential fp32 sum -> divide -> "
-                                   "full sort, as core/function.cpp:150-183, OpenMP over rows"},
+        "config": {"workload": args.workload, "rows_per_gpu": rows, "cols": cols, "k": k, "inv_temperature": inv_t},
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": kind,
+                         "sample": f"one batch of {rows} rows per step; " + what},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -309,6 +346,56 @@ def run_vocab_sharded(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def measure_vocab_sharded(args, rank, world, dev, dist, barrier, max_over_ranks):
+    """The vocabulary-sharded configuration (512 x 256000 bf16, k = 64) as a sub-measurement of the default run:
+    the columns are split evenly over the `world` ranks; a step = partial selection on the local slice, packet
+    exchange (stores into peer memory, or an NCCL all-gather), merge on every rank.  At one GPU the whole matrix
+    is selected on that GPU (no exchange): that time is the T1 of the parallel efficiency T1 / (N * TN)."""
+    from vkop_b200 import sharded, workloads
+
+    name = "sharded_vocab_bf16"
+    rows, cols, dtype, k, inv_t = WORKLOADS[name]
+    lo, hi = sharded.split_even(cols, world, rank)
+    nbuf = 4  # 4 x 262 MB / N per rank: more than the L2 holds at every N up to 8
+    # every rank draws its own slice (the values of a slice do not depend on the others)
+    slices = [workloads.spiked_normal(rows, hi - lo, max(1, 32 // world), 9.0, 1.5, 7000 + 100 * rank + b, dtype).to(dev)
+              for b in range(nbuf)]
+    exchange = "none" if world == 1 else args.exchange
+    try:
+        op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev,
+                                             exchange="peer" if exchange == "peer" else "nccl")
+    except Exception as e:  # peer mapping refused (no peer access between these GPUs): the all-gather still works
+        if exchange != "peer":
+            raise
+        exchange = f"nccl (peer exchange unavailable: {type(e).__name__})"
+        op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev, exchange="nccl")
+    steps = max(5, min(args.steps, 100))
+    for i in range(max(args.warmup, 3)):
+        op(slices[i % nbuf])
+    barrier()
+    # launched from the host, step by step (a collective is not captured into a graph here)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        op(slices[i % nbuf])
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1) / steps)
+    if op.peer is not None:
+        barrier()
+        op.peer.close()
+    esz = slices[0].element_size()
+    nbytes = rows * cols * esz + rows * k * (esz + 4)
+    peak, peak_kind = measured_peak()
+    return {"workload": name, "rows": rows, "cols": cols, "cols_per_gpu": hi - lo, "k": k, "n_gpus": world,
+            "ms_per_step": ms, "steps": steps, "value": rows / (ms * 1e-3), "unit": "rows/s", "scaling": "strong",
+            "exchange": {"none": "none (one GPU holds every column)", "peer": "stores into peer memory + flags (NVLink), then the merge kernel",
+                         "nccl": "NCCL all-gather of per-row packets, then the merge kernel"}.get(exchange, exchange),
+            "launch": "host", "packet_bytes_per_rank": rows * (4 + 2 * k) * 4,
+            "hbm_frac_of_n_gpus": nbytes / (ms * 1e-3) / 1e9 / (peak * world), "peak_kind": peak_kind,
+            "efficiency": "T1 / (N * TN) with T1 = ms_per_step of the one-GPU run of this same sub-measurement"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -322,12 +409,14 @@ def main():
                     help="do not declare the resident inputs ready: every launch fully waits for the one before")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-serialized", action="store_true", help="skip the second loop without VKOP_FLAG_INPUT_READY")
+    ap.add_argument("--no-vocab-sharded", action="store_true", help="skip the vocabulary-sharded sub-measurement")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     ap.add_argument("--sharding", default="rows", choices=["rows", "vocab"],
                     help="N > 1: rows = every rank its own batch (weak scaling, no collective); vocab = the columns of "
                          "one batch split over the ranks, packets all-gathered and merged (strong scaling)")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
-                    help="--sharding vocab: how the packets travel (NCCL all-gather, or stores into peer memory)")
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="vocabulary sharding: how the packets travel (stores into peer memory, or an NCCL all-gather)")
     ap.add_argument("--graph-steps", type=int, default=256, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 
@@ -341,6 +430,8 @@ def main():
         run_reference(args, rank, world)
         return
     args.steps = 2048 if args.steps is None else args.steps
+    if args.steps < 1:
+        raise SystemExit("--steps must be at least 1")
     args.warmup = 20 if args.warmup is None else args.warmup
     if args.workload == "yolo_nms":
         run_nms(args, local_rank)
@@ -355,11 +446,6 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=dev)
 
     rows, cols, dtype, k, inv_t = WORKLOADS[args.workload]
     host = make_inputs(args.workload, 1000 + 100 * rank, "cpu")
@@ -367,68 +453,113 @@ def main():
     values = torch.empty((rows, k), dtype=dtype, device=dev)
     indices = torch.empty((rows, k), dtype=torch.int32, device=dev)
     path = {"auto": capi.PATH_AUTO, "chunk": capi.PATH_CHUNK, "stream": capi.PATH_STREAM, "radix": capi.PATH_RADIX, "bulk": capi.PATH_BULK}[args.path]
-    # the inputs of every step are resident and complete before the timed region starts
-    flags = 0 if args.serialize else capi.FLAG_INPUT_READY
-    desc = capi.make_desc(bufs[0], k, inv_t, splits=args.splits, path=path, flags=flags)
-    ws = capi.Workspace(capi.softmax_topk_workspace_bytes(desc), dev)
 
     import ctypes as C
 
     L = capi.lib()
-    dref = C.byref(desc)
     in_ptrs = [b.data_ptr() for b in bufs]
-    vptr, iptr, wsptr, wsbytes = values.data_ptr(), indices.data_ptr(), ws.ptr, ws.buf.numel()
+    vptr, iptr = values.data_ptr(), indices.data_ptr()
 
-    def step(i, stream):
-        rc = L.vkop_cuda_softmax_topk(dref, in_ptrs[i % NBUF], vptr, iptr, wsptr, wsbytes, stream)
-        if rc != 0:
-            raise capi.VkopError(rc, "softmax_topk")
+    class Loop:
+        """K steps of the operator with one descriptor (its own workspace), captured in a CUDA graph."""
+
+        def __init__(self, flags):
+            self.desc = capi.make_desc(bufs[0], k, inv_t, splits=args.splits, path=path, flags=flags)
+            self.ws = capi.Workspace(capi.softmax_topk_workspace_bytes(self.desc), dev)
+            self.graph, self.gsteps = None, 0
+
+        def step(self, i, stream):
+            rc = L.vkop_cuda_softmax_topk(C.byref(self.desc), in_ptrs[i % NBUF], vptr, iptr, self.ws.ptr, self.ws.buf.numel(), stream)
+            if rc != 0:
+                raise capi.VkopError(rc, "softmax_topk")
+
+        def prepare(self, steps, warmup):
+            stream = torch.cuda.current_stream().cuda_stream
+            for i in range(max(warmup, 3)):
+                self.step(i, stream)
+            torch.cuda.synchronize()
+            if not args.no_graph:
+                # the launch-bound loop is captured once (consecutive steps read different buffers) and replayed
+                self.gsteps = steps if steps <= args.graph_steps else max(NBUF, (args.graph_steps // NBUF) * NBUF)
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                    cs = torch.cuda.current_stream().cuda_stream
+                    for i in range(self.gsteps):
+                        self.step(i, cs)
+                for _ in range(2):  # untimed: more warm-up than asked for
+                    self.graph.replay()
+                torch.cuda.synchronize()
+
+        def run(self, steps):
+            """Enqueues exactly `steps` steps."""
+            stream = torch.cuda.current_stream().cuda_stream
+            done = 0
+            if self.graph is not None:
+                for _ in range(steps // self.gsteps):
+                    self.graph.replay()
+                done = (steps // self.gsteps) * self.gsteps
+            for i in range(done, steps):
+                self.step(i, stream)
+
+    # the inputs of every step are resident and complete before the timed region starts: the main
+    # loop says so (VKOP_FLAG_INPUT_READY); the second loop leaves the flag clear (every call waits)
+    n0 = capi.launch_count()
+    main = Loop(0 if args.serialize else capi.FLAG_INPUT_READY)
+    main.step(0, torch.cuda.current_stream().cuda_stream)
+    launches_per_step = capi.launch_count() - n0
+    main.prepare(args.steps, args.warmup)
+    waiting = None
+    if not args.serialize and not args.no_serialized:
+        waiting = Loop(0)
+        waiting.prepare(args.steps, args.warmup)
+
+    # graphs are captured before the process group exists (its watchdog thread must not meet a capture)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    stream = torch.cuda.current_stream().cuda_stream
-    n0 = capi.launch_count()
-    step(0, stream)
-    launches_per_step = capi.launch_count() - n0
-    for i in range(max(args.warmup, 3)):
-        step(i, stream)
-    barrier()
-    graph = None
-    gsteps = max(NBUF, (args.graph_steps // NBUF) * NBUF)
-    if not args.no_graph and args.steps >= gsteps:
-        # the launch-bound loop is captured once (consecutive steps read different buffers) and replayed
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            cs = torch.cuda.current_stream().cuda_stream
-            for i in range(gsteps):
-                step(i, cs)
-        for _ in range(3):
-            graph.replay()
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(loop, steps, sampler=None):
         barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.start()
+        e0.record()
+        loop.run(steps)
+        e1.record()
+        if sampler:
+            sampler.sample_now()  # the queued steps are still running: one sample even when the region is shorter than a period
+        barrier()
+        if sampler:
+            sampler.stop()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
     sampler = ClockSampler(local_rank)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    e0.record()
-    done = 0
-    if graph is not None:
-        for _ in range(args.steps // gsteps):
-            graph.replay()
-        done = (args.steps // gsteps) * gsteps
-    for i in range(done, args.steps):
-        step(i, stream)
-    e1.record()
-    sampler.sample_now()  # the queued steps are still running: one sample even when the region is shorter than a period
-    barrier()
-    sampler.stop()
+    ms_max = timed(main, args.steps, sampler)
     launches = launches_per_step * args.steps
-    ms = e0.elapsed_time(e1) / args.steps
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+    graph = main.graph
+    gsteps = main.gsteps
+    serialized = None
+    if waiting is not None:
+        ms_w = timed(waiting, args.steps)
+        serialized = {"ms_per_step": ms_w, "value": rows * world / (ms_w * 1e-3), "unit": "rows/s",
+                      "input_ready_flag": False, "ratio_to_overlapping": ms_w / ms_max}
+
+    vocab_sharded = None
+    if not args.no_vocab_sharded and args.workload == "llm_vocab_f32":
+        vocab_sharded = measure_vocab_sharded(args, rank, world, dev, dist, barrier, max_over_ranks)
 
     # ---- end to end: pinned host logits -> device -> operator -> results to host, every step ----
     e2e = None
@@ -455,40 +586,43 @@ def main():
         for i in range(e2e_steps):
             e2e_step(i)
         barrier()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
         esz = bufs[0].element_size()
-        e2e = {"value": rows * world / (float(t.item()) * 1e-3), "unit": "rows/s",
+        e2e = {"value": rows * world / (e2e_ms * 1e-3), "unit": "rows/s",
                "h2d_bytes_per_step": rows * cols * esz, "d2h_bytes_per_step": rows * k * (esz + 4),
-               "steps": e2e_steps, "ms_per_step": float(t.item()),
+               "steps": e2e_steps, "ms_per_step": e2e_ms,
                "api": "vkop_host_pipeline_run (C++ Runtime::RegisterPostProcess Softmax+TopK, host buffers)"}
 
-    # ---- parity spot check of the last step against the oracle (outside every timed region) ----
+    # ---- parity spot check of one more step against the oracle (outside every timed region), then
+    # the CPU baselines on a bounded sample ----
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
-        from tests.util import ORACLE_DTYPE, to_oracle_array
 
-        xa = to_oracle_array(host[0])
-        oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
-        # parity spot check: one more step on buffer 0, indices against the oracle, bit for bit
-        step(0, stream)
+        xa = oracle.to_oracle_array(host[0])
+        main.step(0, torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
-        _, want_idx = oracle.softmax_topk(xa, k, inv_t, dtype=ORACLE_DTYPE[dtype])
+        _, want_idx = oracle.softmax_topk(xa, k, inv_t, dtype=oracle.oracle_dtype(dtype))
         if not (indices.cpu().numpy() == want_idx).all():
             raise SystemExit("bench.py: the GPU result differs from the oracle")
+        step_cpu, cores, kind, what = cpu_reference_step(args.workload)
         reps, t0 = 0, time.perf_counter()
         while reps < 10 or time.perf_counter() - t0 < 2.0:  # a bounded sample: about 2 s on all cores
-            oracle.softmax_topk(xa, k, inv_t, dtype=ORACLE_DTYPE[dtype], sum_mode=oracle.SUM_F32_SEQUENTIAL,
-                                full_sort=True)
+            step_cpu()
             reps += 1
         dt = (time.perf_counter() - t0) / reps
-        cpu_baseline = {"value": rows / dt, "unit": "rows/s", "cores": oracle.num_threads(), "kind": "port",
-                        "sample": f"{reps} passes over one batch of {rows} rows ({dt * reps:.1f} s wall): max -> exp -> "
-                                  "sequential fp32 sum -> divide -> full sort (core/function.cpp:150-183), "
-                                  "OpenMP over rows"}
+        cpu_baseline = {"value": rows / dt, "unit": "rows/s", "cores": cores, "kind": kind,
+                        "sample": f"{reps} passes over one batch of {rows} rows ({dt * reps:.1f} s wall): " + what}
+        # torch-CPU softmax + topk, the oracle the reference's own tests use (tests/TopkTest.cpp:73, tests/SoftmaxTest.cpp:138)
+        torch.set_num_threads(cores)
+        xt = host[0].float()
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or time.perf_counter() - t0 < 2.0:
+            torch.topk(torch.softmax(xt * inv_t, dim=1), k, dim=1)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        cpu_baseline["torch_cpu"] = {"value": rows / dt, "unit": "rows/s", "cores": cores,
+                                     "sample": f"{reps} passes of torch.softmax + torch.topk on one batch, {torch.get_num_threads()} threads"}
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -504,8 +638,9 @@ def main():
                        "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * cols * bufs[0].element_size() >> 20} MiB) > L2",
                        "path": args.path, "input_ready_flag": not args.serialize, "launch": "host" if graph is None else f"cuda graph of {gsteps} steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": peak_kind,
+                         "traffic": ncu_traffic_bytes(args.workload), "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": abytes, "pct_of_8TBs": achieved / 8000.0 * 100.0},
+            "serialized": serialized, "vocab_sharded": vocab_sharded,
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": sampler.summary(),
         }

@@ -225,6 +225,23 @@ def ref_unfused_softmax_topk(logits: np.ndarray, k: int, inv_temperature: float 
     return np.take_along_axis(p, order, axis=1), order.astype(np.int64)
 
 
+def to_oracle_array(x) -> np.ndarray:
+    """CPU torch tensor -> numpy array in the oracle's storage convention (16-bit types as uint16 bits)."""
+    import torch
+
+    x = x.detach().cpu()
+    if x.dtype == torch.float32:
+        return x.numpy()
+    return x.view(torch.int16).numpy().view(np.uint16)
+
+
+def oracle_dtype(torch_dtype) -> int:
+    """The oracle's dtype tag of a torch dtype."""
+    import torch
+
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[torch_dtype]
+
+
 def order_key(x: float) -> int:
     return int(lib().oracle_order_key(C.c_float(x)))
 

@@ -12,14 +12,7 @@ import oracle
 #   bf16 logits: 8e-3 relative (three mantissa bits fewer than fp16)
 TOL = {torch.float32: (1e-6, 1e-5), torch.float16: (6e-8, 2e-3), torch.bfloat16: (1e-30, 8e-3)}
 ORACLE_DTYPE = {torch.float32: oracle.F32, torch.float16: oracle.F16, torch.bfloat16: oracle.BF16}
-
-
-def to_oracle_array(x: torch.Tensor) -> np.ndarray:
-    """CPU torch tensor -> numpy array in the oracle's storage convention (16-bit types as uint16 bits)."""
-    x = x.detach().cpu()
-    if x.dtype == torch.float32:
-        return x.numpy()
-    return x.view(torch.int16).numpy().view(np.uint16)
+to_oracle_array = oracle.to_oracle_array
 
 
 def oracle_softmax_topk(x: torch.Tensor, k: int, inv_temperature: float = 1.0, value_kind=oracle.VALUE_PROBABILITY):
