@@ -184,6 +184,16 @@ int vkop_cuda_packets_push(const void *packets, size_t packets_bytes, void *cons
                            int32_t rank, int32_t world, uint32_t seq, void *tickets, void *stream);
 int vkop_cuda_packets_wait(const void *flags, int32_t world, uint32_t seq, uint32_t max_polls, int32_t *status,
                            void *stream);
+/* One exchange step of ALL ranks in a single cooperative launch, for a machine with fewer GPUs than
+ * ranks (tests, bring-up): kernels that wait for one another must not be separate launches on one GPU,
+ * so rank r's push and rank r's bounded wait are block groups of one kernel whose blocks are all
+ * resident.  packets_of / tickets_of: DEVICE arrays of `world` device pointers (rank r's packets and
+ * tickets); peer_slots / peer_flags as above; status: `world` words, status[r] receives VKOP_TIMEOUT
+ * if rank r's wait runs out.  VKOP_UNSUPPORTED when the blocks would not all fit the GPU at once.
+ * No counterpart in the reference. */
+int vkop_cuda_packets_exchange_all_ranks(const void *const *packets_of, size_t packets_bytes, void *const *peer_slots,
+                                         void *const *peer_flags, int32_t world, uint32_t seq, void *const *tickets_of,
+                                         uint32_t max_polls, int32_t *status, void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* NMS (ONNX NonMaxSuppression) per (batch, class).
@@ -239,8 +249,10 @@ int vkop_cuda_yolo_nms(const vkop_nms_desc *desc, const void *head, int32_t *out
  * VKOP_WORKSPACE_TOO_SMALL when the shape needs more scratch than the array
  * holds.  The first call on a device looks up the array's device address and
  * should come before any stream capture on that device.  All calls on a
- * device share the array: calls that overlap on the GPU race on it, so order
- * them (one stream, or events), or use the workspace entry point. */
+ * device share the array, which keeps what the last call left: every call
+ * first clears the counters it uses, on its stream.  Calls that overlap on
+ * the GPU race on the array, so order them (one stream, or events), or use
+ * the workspace entry point. */
 size_t vkop_cuda_static_scratch_bytes(void);
 int vkop_cuda_softmax_topk_static(const vkop_softmax_topk_desc *desc, const void *logits, void *out_values,
                                   void *out_indices, void *stream);

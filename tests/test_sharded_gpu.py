@@ -141,3 +141,40 @@ def test_peer_exchange_kernels_with_emulated_ranks():
             util.assert_probs_close(v, wv, x.dtype, f"emulated rank {r}, step {seq}")
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+def test_all_ranks_exchange_in_one_launch():
+    """Four ranks on one GPU with their pushes and waits running CONCURRENTLY: one cooperative launch in which
+    every rank's blocks store its packets into all receive buffers and raise the flags while the ranks'
+    waiting blocks already poll theirs (the release / acquire pairing of the real exchange; separate
+    launches that wait for one another are not allowed on one GPU).  512 rows, the row count of the
+    vocabulary-sharded configuration; results of every rank against the oracle, over several steps; the
+    bounded waits must not run out."""
+    from tests import util
+    from vkop_b200 import capi, workloads
+    from vkop_b200.sharded import split_even
+
+    world, rows, k = 4, 512, 64
+    words = capi.packet_bytes(k) // 4
+    dev = torch.device("cuda")
+    slots = [torch.zeros((2, world, rows, words), dtype=torch.int32, device=dev) for _ in range(world)]
+    flags = [torch.zeros((2, world), dtype=torch.int32, device=dev) for _ in range(world)]
+    tickets = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    status = torch.zeros(world, dtype=torch.int32, device=dev)
+    packets = [torch.empty((rows, words), dtype=torch.int32, device=dev) for _ in range(world)]
+    ptr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    slot_ptrs, flag_ptrs, ticket_ptrs, packet_ptrs = ptr(slots), ptr(flags), ptr(tickets), ptr(packets)
+    for seq in range(1, 5):
+        x = workloads.sharded_vocab(rows=rows, cols=64000, seed=40 + seq)
+        xg = x.cuda()
+        for r in range(world):
+            lo, hi = split_even(x.shape[1], world, r)
+            capi.softmax_topk_partial(xg[:, lo:hi].contiguous(), k, lo, packets=packets[r])
+        capi.packets_exchange_all_ranks(packet_ptrs, rows * words * 4, slot_ptrs, flag_ptrs, world, seq, ticket_ptrs, status,
+                                        max_polls=200000)
+        wv, wi = util.oracle_softmax_topk(x, k)
+        for r in range(world):
+            v, i = capi.softmax_topk_merge(slots[r][seq & 1], rows, k, x.dtype)
+            util.assert_indices_equal(i, wi, f"rank {r}, step {seq}")
+            util.assert_probs_close(v, wv, x.dtype, f"rank {r}, step {seq}")
+        assert status.cpu().tolist() == [0] * world, "a bounded wait ran out"

@@ -33,6 +33,13 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(capi):
     torch.cuda.synchronize()
     assert _same(got1, want1)
     assert _same(got2, want2)
+    # and against the CPU oracle (indices bit for bit, probabilities within the fp32 tolerance)
+    from tests import util
+
+    for x, got in ((x1, got1), (x2, got2)):
+        wv, wi = util.oracle_softmax_topk(x.cpu(), 50, 1.25)
+        util.assert_indices_equal(got[1], wi, "static entry point")
+        util.assert_probs_close(got[0], wv, torch.float32, "static entry point")
 
 
 def test_descriptor_change_clears_what_it_must(capi):
@@ -46,6 +53,20 @@ def test_descriptor_change_clears_what_it_must(capi):
         torch.cuda.synchronize()
         assert _same(got, want), (rows, cols, k)
         assert _same(again, want), (rows, cols, k)
+
+
+def test_shapes_alternate_on_the_shared_array(capi):
+    """Calls with different launch shapes lay their counters out differently in the one array; every call
+    clears its own first, so they may alternate freely."""
+    x = workloads.llm_vocab(seed=9, rows=16).cuda()
+    y = torch.randn(3, 300007, generator=torch.Generator().manual_seed(10)).cuda()
+    wx = capi.softmax_topk(x, 50, 1.25, path=capi.PATH_CHUNK)
+    wy = capi.softmax_topk(y, 64, path=capi.PATH_CHUNK)
+    for _ in range(3):
+        gx = capi.softmax_topk_static(x, 50, 1.25)
+        gy = capi.softmax_topk_static(y, 64)
+        torch.cuda.synchronize()
+        assert _same(gx, wx) and _same(gy, wy)
 
 
 def test_limits_are_reported(capi):

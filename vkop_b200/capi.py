@@ -27,7 +27,7 @@ EXPORTS = [
     "vkop_cuda_packet_bytes", "vkop_cuda_softmax_topk_partial", "vkop_cuda_softmax_topk_merge",
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
     "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
-    "vkop_cuda_packets_push", "vkop_cuda_packets_wait", "vkop_cuda_yolo_nms",
+    "vkop_cuda_packets_push", "vkop_cuda_packets_wait", "vkop_cuda_packets_exchange_all_ranks", "vkop_cuda_yolo_nms",
     "vkop_cuda_sample_topk",
 ]
 
@@ -82,6 +82,7 @@ def lib() -> C.CDLL:
         L.vkop_cuda_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_packets_push.argtypes = [vp, sz, vp, vp, C.c_int32, C.c_int32, C.c_uint32, vp, vp]
         L.vkop_cuda_packets_wait.argtypes = [vp, C.c_int32, C.c_uint32, C.c_uint32, vp, vp]
+        L.vkop_cuda_packets_exchange_all_ranks.argtypes = [vp, sz, vp, vp, C.c_int32, C.c_uint32, vp, C.c_uint32, vp, vp]
         L.vkop_cuda_yolo_nms.argtypes = [C.POINTER(NmsDesc), vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_sample_topk.argtypes = [vp, C.c_int32, vp, C.c_int32, C.c_int64, C.c_int32, C.c_float, vp, vp, vp, vp]
         L.vkop_cuda_static_scratch_bytes.restype = sz
@@ -223,6 +224,15 @@ def packets_push(packets: torch.Tensor, peer_slots: torch.Tensor, peer_flags: to
 
 def packets_wait(flags: torch.Tensor, world: int, seq: int, status: torch.Tensor, max_polls: int = 1 << 20) -> None:
     check(lib().vkop_cuda_packets_wait(flags.data_ptr(), world, seq, max_polls, status.data_ptr(), _stream()), "packets_wait")
+
+
+def packets_exchange_all_ranks(packet_ptrs: torch.Tensor, packets_bytes: int, peer_slots: torch.Tensor, peer_flags: torch.Tensor,
+                               world: int, seq: int, ticket_ptrs: torch.Tensor, status: torch.Tensor, max_polls: int = 1 << 20) -> None:
+    """Every rank's push and bounded wait of one step in one cooperative launch (ranks emulated on one GPU).
+    packet_ptrs / ticket_ptrs / peer_slots / peer_flags: int64 CUDA tensors of one device pointer per rank."""
+    check(lib().vkop_cuda_packets_exchange_all_ranks(packet_ptrs.data_ptr(), packets_bytes, peer_slots.data_ptr(), peer_flags.data_ptr(),
+                                                     world, seq, ticket_ptrs.data_ptr(), max_polls, status.data_ptr(), _stream()),
+          "packets_exchange_all_ranks")
 
 
 def static_scratch_bytes() -> int:

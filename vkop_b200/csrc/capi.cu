@@ -297,6 +297,16 @@ int vkop_cuda_packets_wait(const void *flags, int32_t world, uint32_t seq, uint3
     return launch_packets_wait(flags, world, seq, max_polls, status, static_cast<cudaStream_t>(stream));
 }
 
+int vkop_cuda_packets_exchange_all_ranks(const void *const *packets_of, size_t packets_bytes, void *const *peer_slots,
+                                         void *const *peer_flags, int32_t world, uint32_t seq, void *const *tickets_of,
+                                         uint32_t max_polls, int32_t *status, void *stream) {
+    if (!packets_of || !peer_slots || !peer_flags || !tickets_of || !status || world < 1 || world > 32 || seq == 0 ||
+        max_polls == 0 || packets_bytes % 4 != 0)
+        return VKOP_INVALID_ARG;
+    return launch_packets_exchange_all_ranks(packets_of, packets_bytes, peer_slots, peer_flags, world, seq, tickets_of, max_polls,
+                                             status, static_cast<cudaStream_t>(stream));
+}
+
 // ---------------------------------------------------------------------------
 // Fused Softmax + TopK without a caller workspace.
 //
@@ -319,31 +329,19 @@ int vkop_cuda_packets_wait(const void *flags, int32_t world, uint32_t seq, uint3
 //     (cudaGetSymbolAddress, with that device current) and should therefore
 //     come before any stream capture on that device;
 //   - all calls on a device share the one array and it keeps what the last
-//     call left there.  The kernels return their counters to zero; when the
-//     descriptor differs from the previous call's, the part of the array the
-//     new call uses is cleared first, on the call's stream.  Calls that
-//     overlap on the GPU (different streams without an ordering between them)
-//     race on the array: give them an order, or use the workspace entry point.
+//     call left there: every call first clears the few hundred bytes of
+//     counters its launch shape uses, on the call's stream (no allocation),
+//     whatever ran before.  Calls that overlap on the GPU
+//     (different streams without an ordering between them) race on the array:
+//     give them an order, or use the workspace entry point.
 namespace {
 constexpr size_t kStaticScratchBytes = 4u << 20;
 constexpr int kStaticMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-struct StaticScratchState {
-    void *ptr = nullptr;   // device address of g_static_scratch on this device (not the host-side symbol)
-    uint64_t key = 0;      // descriptor the array last served (0: none yet)
-};
-StaticScratchState g_static_state[kStaticMaxDevices];
+// device address of g_static_scratch per device (not the host-side symbol), looked up once
+void *g_static_ptr[kStaticMaxDevices] = {};
 std::mutex g_static_mutex;
-
-uint64_t static_desc_key(const vkop_softmax_topk_desc &d) {
-    uint64_t h = 1469598103934665603ull;
-    const uint64_t parts[] = {static_cast<uint64_t>(d.rows), static_cast<uint64_t>(d.cols), static_cast<uint64_t>(d.row_stride),
-                              static_cast<uint64_t>(d.dtype), static_cast<uint64_t>(d.k), static_cast<uint64_t>(d.splits)};
-    for (uint64_t v : parts)
-        h = (h ^ v) * 1099511628211ull;
-    return h | 1ull;
-}
 }  // namespace
 
 size_t vkop_cuda_static_scratch_bytes(void) { return kStaticScratchBytes; }
@@ -367,31 +365,35 @@ int vkop_cuda_softmax_topk_static(const vkop_softmax_topk_desc *desc, const void
         return VKOP_CUDA_ERROR;
     if (dev < 0 || dev >= kStaticMaxDevices)
         return VKOP_UNSUPPORTED;
-    std::lock_guard<std::mutex> lock(g_static_mutex);
-    StaticScratchState &st = g_static_state[dev];
-    if (!st.ptr) {
-        // once per device, with that device current: the symbol's address on THIS device
-        void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
-            cudaGetLastError();
-            return VKOP_CUDA_ERROR;
+    void *ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_ptr[dev]) {
+            // once per device, with that device current: the symbol's address on THIS device
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+                cudaGetLastError();
+                return VKOP_CUDA_ERROR;
+            }
+            g_static_ptr[dev] = p;
         }
-        st.ptr = p;
-        st.key = 0;
+        ptr = g_static_ptr[dev];
     }
-    const uint64_t key = static_desc_key(d);
-    if (st.key != key) {
-        // counters of this layout must start at zero; the array holds whatever the last call left
-        if (need > 0 && cudaMemsetAsync(st.ptr, 0, need, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
-            cudaGetLastError();
-            return VKOP_CUDA_ERROR;
-        }
-        st.key = key;
-    }
-    rc = vkop_cuda_softmax_topk(&d, logits, out_values, out_indices, st.ptr, kStaticScratchBytes, stream);
+    // The counters of this launch shape must start at zero and the array holds whatever the last
+    // call (of any shape, finished or failed) left: clear them every time.  The lists behind them
+    // are written before they are read.
+    SelectPlan plan;
+    rc = plan_select(d, logits, &plan);
     if (rc != VKOP_OK)
-        st.key = 0;  // nothing is known about the array's contents after a failed call
-    return rc;
+        return rc;
+    if (plan.kind != kSelectChunk)
+        return VKOP_UNSUPPORTED;
+    if (plan.chunk.counters_bytes > 0 &&
+        cudaMemsetAsync(ptr, 0, plan.chunk.counters_bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return VKOP_CUDA_ERROR;
+    }
+    return vkop_cuda_softmax_topk(&d, logits, out_values, out_indices, ptr, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

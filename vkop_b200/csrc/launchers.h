@@ -92,5 +92,9 @@ int launch_sample_topk(const void *values, int dtype, const void *indices, int i
 int launch_packets_push(const void *packets, size_t bytes, void *const *peer_slots, void *const *peer_flags, int rank,
                         int world, uint32_t seq, void *tickets, cudaStream_t stream);
 int launch_packets_wait(const void *flags, int world, uint32_t seq, uint32_t max_polls, int *status, cudaStream_t stream);
+// every rank's push and wait of one step in a single cooperative launch (ranks emulated on one GPU)
+int launch_packets_exchange_all_ranks(const void *const *srcs, size_t bytes, void *const *peer_slots, void *const *peer_flags,
+                                      int world, uint32_t seq, void *const *tickets, uint32_t max_polls, int *status,
+                                      cudaStream_t stream);
 
 }  // namespace vkop_cuda
