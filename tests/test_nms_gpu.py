@@ -98,6 +98,77 @@ def test_large_candidate_sets(capi):
     run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05, pre_topk=1500, max_output_boxes_per_class=100)
 
 
+def test_iou_next_to_the_threshold(capi):
+    """Integer boxes give IoUs that are exact ratios (1/3, 1/2, 3/5 ...); with the threshold on such a ratio, one
+    float above and one below, the test that avoids the division has to hand over to the exact one."""
+    boxes = []
+    for x in range(12):
+        for w in (2, 3, 4, 6):
+            boxes.append([x, 0.0, x + w, 1.0])
+            boxes.append([x, 0.0, x + w, 2.0])
+    boxes = torch.tensor(boxes, dtype=torch.float32)[None]
+    N = boxes.shape[1]
+    g = torch.Generator().manual_seed(44)
+    scores = torch.rand(1, 3, N, generator=g) * 0.9 + 0.05
+    for ratio in (1 / 3, 0.5, 0.6, 0.25, 2 / 3, 0.2, 0.75):
+        t = np.float32(ratio)
+        for thr in (t, np.nextafter(t, np.float32(1)), np.nextafter(t, np.float32(0))):
+            run_both(capi, boxes, scores, iou_threshold=float(thr), score_threshold=0.0)
+
+
+def test_areas_and_thresholds_outside_the_quick_range(capi):
+    """Huge and tiny boxes (areas beyond 1e28 / below 1e-28), thresholds of 0, below 0 and tiny, boxes with NaN
+    or infinite coordinates: all of these take the exact IoU."""
+    g = torch.Generator().manual_seed(45)
+    N = 200
+    xy = torch.rand(1, N, 2, generator=g) * 10
+    wh = torch.rand(1, N, 2, generator=g) * 6 + 0.5
+    base = torch.cat([xy, xy + wh], -1)
+    scores = torch.rand(1, 2, N, generator=g)
+    for scale in (1e16, 1e-16, 1e19, 1e-19):
+        run_both(capi, base * scale, scores, iou_threshold=0.5, score_threshold=0.1)
+    mixed = base.clone()
+    mixed[0, ::3] *= 1e15
+    run_both(capi, mixed, scores, iou_threshold=0.4, score_threshold=0.1)
+    for thr in (0.0, -0.5, 1e-7, 1e-30, 5.0):
+        run_both(capi, base, scores, iou_threshold=thr, score_threshold=0.1)
+    odd = base.clone()
+    odd[0, 3, 0] = float("nan")
+    odd[0, 10, 2] = float("inf")
+    odd[0, 17] = torch.tensor([float("-inf"), 0.0, float("inf"), 5.0])
+    odd[0, 21, 3] = float("nan")
+    run_both(capi, odd, scores, iou_threshold=0.5, score_threshold=0.1)
+
+
+def test_candidate_counts_around_the_sort_limits(capi):
+    """Lists of 511 .. 513 candidates (register sort / shared-memory sort), an odd number of ordered boxes (the mask
+    takes rows in pairs), lists cut down before the sort, and all scores tied (the cut then reaches the index bits)."""
+    g = torch.Generator().manual_seed(46)
+    for N in (127, 128, 129, 511, 512, 513):
+        xy = torch.rand(1, N, 2, generator=g) * 200
+        wh = torch.rand(1, N, 2, generator=g) * 30 + 1
+        boxes = torch.cat([xy, xy + wh], -1)
+        scores = torch.rand(1, 2, N, generator=g) * 0.9 + 0.1
+        run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05)
+    N = 1000
+    xy = torch.rand(1, N, 2, generator=g) * 300
+    wh = torch.rand(1, N, 2, generator=g) * 40 + 1
+    boxes = torch.cat([xy, xy + wh], -1)
+    scores = torch.rand(1, 3, N, generator=g) * 0.9 + 0.1
+    for pre in (256, 300, 301, 511, 512):
+        run_both(capi, boxes, scores, iou_threshold=0.5, score_threshold=0.05, pre_topk=pre)
+    tied = torch.full((1, 2, N), 0.5)
+    tied[0, 1, ::2] = 0.75
+    for pre in (100, 301):
+        run_both(capi, boxes, tied, iou_threshold=0.5, score_threshold=0.05, pre_topk=pre)
+    # more candidates than scan slots (1024) and a tie across the cut
+    N = 1500
+    xy = torch.rand(1, N, 2, generator=g) * 300
+    boxes = torch.cat([xy, xy + 20], -1)
+    tied = torch.full((1, 1, N), 0.5)
+    run_both(capi, boxes, tied, iou_threshold=0.5, score_threshold=0.05, pre_topk=300)
+
+
 def test_capacity_and_repeat(capi):
     boxes, scores = workloads.yolo_detect(batch=1, classes=4)
     kw = dict(workloads.YOLO_PARAMS)
