@@ -118,6 +118,31 @@ int vkop_cuda_softmax_topk(const vkop_softmax_topk_desc *desc, const void *logit
 int vkop_cuda_topk(const vkop_softmax_topk_desc *desc, const void *input, void *out_values, void *out_indices,
                    void *workspace, size_t workspace_bytes, void *stream);
 
+/* TopK along any axis, and the unsorted output order.  The input is viewed
+ * row-major as [outer, axis_len, inner] and the k best along the middle axis
+ * go to out_values / out_indices viewed as [outer, k, inner] (the input's
+ * shape with shape[axis] = k, as ops/Topk.hpp:108-109 sizes the outputs).
+ * Replaces ops/Topk.hpp:62-79 (attributes "axis", "sorted") and :98-103;
+ * the reference's shader only ever selects along the last axis of a 1-D or
+ * 2-D tensor (shaders/topk.comp:119-175) and ignores "sorted".
+ * sorted != 0: best first, as vkop_cuda_topk.  sorted == 0: the same k
+ * entries in ascending index order.  Indices run from 0 to axis_len - 1. */
+typedef struct vkop_topk_axis_desc {
+    int64_t outer;
+    int64_t axis_len;
+    int64_t inner;
+    int32_t dtype;       /* vkop_dtype of the input and of the output values */
+    int32_t k;           /* 1 <= k <= min(axis_len, 4096) */
+    int32_t index_dtype; /* vkop_index_dtype */
+    int32_t largest;     /* 1 = largest, 0 = smallest */
+    int32_t sorted;      /* 0 = ascending index order */
+    int32_t path;        /* vkop_select_path for the selection itself */
+} vkop_topk_axis_desc;
+
+int vkop_cuda_topk_axis_workspace(const vkop_topk_axis_desc *desc, size_t *bytes);
+int vkop_cuda_topk_axis(const vkop_topk_axis_desc *desc, const void *input, void *out_values, void *out_indices,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* Unfused Softmax with the full probability tensor as output, along the
  * middle axis of a row-major [outer, axis_len, inner] view (inner = 1 for the

@@ -117,6 +117,48 @@ static void test_topk(Env &env) {
     }
 }
 
+static void test_topk_axis_and_order(Env &env) {
+    // ops/Topk.hpp:62-79, 98-103: "axis" 0 .. 2 and "sorted"; expectation = the oracle's TopK on the same view
+    struct Case {
+        std::vector<int> shape;
+        int axis, k, largest, sorted;
+    };
+    const std::vector<Case> cases = {{{3, 2000}, 0, 2, 1, 1},     {{3, 2000}, 0, 3, 0, 0},  {{4, 50, 33}, 1, 7, 1, 1},
+                                     {{4, 50, 33}, 1, 7, 1, 0},   {{2, 300, 5}, -2, 9, 0, 1}, {{5, 64, 40}, 0, 3, 1, 0},
+                                     {{3, 2000}, -1, 7, 1, 0},    {{2, 6, 1000}, 2, 11, 0, 0}};
+    for (const auto &c : cases) {
+        Lcg rng(77);
+        auto input = std::make_shared<Tensor<float>>(c.shape);
+        for (int64_t i = 0; i < input->num_elements(); i++)
+            (*input)[i] = std::round(rng.normal() * 8.0f) / 8.0f;  // ties
+        auto values = std::make_shared<Tensor<float>>(true);
+        auto indices = std::make_shared<Tensor<int>>(true);
+        run_op(env, "TopK", {input}, {values, indices},
+               {{"k", std::to_string(c.k)}, {"axis", std::to_string(c.axis)}, {"largest", std::to_string(c.largest)},
+                {"sorted", std::to_string(c.sorted)}});
+        values->copyToCPU(env.cmdpool);
+        indices->copyToCPU(env.cmdpool);
+        const int rank = static_cast<int>(c.shape.size());
+        const int axis = c.axis < 0 ? c.axis + rank : c.axis;
+        std::vector<int> want_shape = c.shape;
+        want_shape[axis] = c.k;
+        EXPECT(values->getShape() == want_shape && indices->getShape() == want_shape, "TopK axis %d output shape", c.axis);
+        int64_t outer = 1, inner = 1;
+        for (int i = 0; i < axis; i++)
+            outer *= c.shape[i];
+        for (int i = axis + 1; i < rank; i++)
+            inner *= c.shape[i];
+        std::vector<float> wv(static_cast<size_t>(outer * inner * c.k));
+        std::vector<int64_t> wi(wv.size());
+        oracle_topk(input->data(), 0, outer, c.shape[axis], inner, c.k, c.largest, c.sorted, wv.data(), wi.data());
+        for (size_t i = 0; i < wv.size(); i++) {
+            EXPECT((*indices)[i] == static_cast<int>(wi[i]), "TopK axis %d sorted %d index %zu: %d vs %lld", c.axis, c.sorted, i,
+                   (*indices)[i], static_cast<long long>(wi[i]));
+            EXPECT((*values)[i] == wv[i], "TopK axis %d value %zu", c.axis, i);
+        }
+    }
+}
+
 static void test_softmax(Env &env) {
     // tests/SoftmaxTest.cpp:195-202
     const std::vector<std::tuple<std::vector<int>, int>> cases = {{{1, 10, 7, 7}, 1}, {{1, 6, 8, 8}, 3}, {{2, 4, 10, 10}, 2},
@@ -272,6 +314,7 @@ int main() {
     Env env;
     std::printf("device: %s\n", env.dev->getDeviceName().c_str());
     test_topk(env);
+    test_topk_axis_and_order(env);
     test_softmax(env);
     test_nms(env);
     test_runtime_pipeline(env);

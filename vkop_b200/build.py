@@ -14,7 +14,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libvkop_cuda.so")
-SOURCES = ["capi.cu", "softmax_topk.cu", "softmax_topk_stream.cu", "softmax_topk_bulk.cu", "radix_select.cu", "softmax.cu", "nms.cu",
+SOURCES = ["capi.cu", "softmax_topk.cu", "softmax_topk_stream.cu", "softmax_topk_bulk.cu", "topk_axis.cu", "radix_select.cu", "softmax.cu", "nms.cu",
            "peer_exchange.cu", "sample.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wextra", "-I", os.path.join(ROOT, "include"), "-I", CSRC]

@@ -28,7 +28,7 @@ EXPORTS = [
     "vkop_cuda_nms_workspace", "vkop_cuda_nms",
     "vkop_cuda_static_scratch_bytes", "vkop_cuda_softmax_topk_static",
     "vkop_cuda_packets_push", "vkop_cuda_packets_wait", "vkop_cuda_packets_exchange_all_ranks", "vkop_cuda_yolo_nms",
-    "vkop_cuda_sample_topk",
+    "vkop_cuda_sample_topk", "vkop_cuda_topk_axis_workspace", "vkop_cuda_topk_axis",
 ]
 
 
@@ -42,6 +42,12 @@ class SoftmaxTopkDesc(C.Structure):
 class SoftmaxDesc(C.Structure):
     _fields_ = [("outer", C.c_int64), ("axis_len", C.c_int64), ("inner", C.c_int64), ("dtype", C.c_int32),
                 ("inv_temperature", C.c_float)]
+
+
+class TopkAxisDesc(C.Structure):
+    _fields_ = [("outer", C.c_int64), ("axis_len", C.c_int64), ("inner", C.c_int64), ("dtype", C.c_int32),
+                ("k", C.c_int32), ("index_dtype", C.c_int32), ("largest", C.c_int32), ("sorted", C.c_int32),
+                ("path", C.c_int32)]
 
 
 class NmsDesc(C.Structure):
@@ -76,6 +82,8 @@ def lib() -> C.CDLL:
         L.vkop_cuda_softmax_topk.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_topk.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_softmax.argtypes = [C.POINTER(SoftmaxDesc), vp, vp, vp]
+        L.vkop_cuda_topk_axis_workspace.argtypes = [C.POINTER(TopkAxisDesc), C.POINTER(sz)]
+        L.vkop_cuda_topk_axis.argtypes = [C.POINTER(TopkAxisDesc), vp, vp, vp, vp, sz, vp]
         L.vkop_cuda_softmax_topk_partial.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, vp, vp, sz, vp]
         L.vkop_cuda_softmax_topk_merge.argtypes = [C.POINTER(SoftmaxTopkDesc), vp, C.c_int32, vp, vp, vp]
         L.vkop_cuda_nms_workspace.argtypes = [C.POINTER(NmsDesc), C.POINTER(sz)]
@@ -168,6 +176,30 @@ def softmax_topk(logits: torch.Tensor, k: int, inv_temperature: float = 1.0, ind
     fn = lib().vkop_cuda_topk if standalone_topk else lib().vkop_cuda_softmax_topk
     check(fn(C.byref(desc), logits.data_ptr(), values.data_ptr(), indices.data_ptr(), workspace.ptr,
              workspace.buf.numel(), _stream()), "topk" if standalone_topk else "softmax_topk")
+    return values, indices
+
+
+def topk_axis(x: torch.Tensor, k: int, axis: int = -1, largest: bool = True, sorted: bool = True, index_dtype: int = I32,
+              path: int = PATH_AUTO, workspace: Workspace | None = None):
+    """TopK of a contiguous CUDA tensor along any axis.  Returns (values, indices) shaped like x with shape[axis] = k;
+    sorted=False gives the k entries in ascending index order."""
+    if not x.is_cuda or not x.is_contiguous():
+        raise RuntimeError("vkop_b200 runs on contiguous CUDA device memory only")
+    axis = axis % x.dim()
+    outer = int(torch.Size(x.shape[:axis]).numel())
+    inner = int(torch.Size(x.shape[axis + 1:]).numel())
+    desc = TopkAxisDesc(outer=outer, axis_len=x.shape[axis], inner=inner, dtype=dtype_tag(x), k=k, index_dtype=index_dtype,
+                        largest=int(largest), sorted=int(sorted), path=path)
+    n = C.c_size_t(0)
+    check(lib().vkop_cuda_topk_axis_workspace(C.byref(desc), C.byref(n)), "topk_axis_workspace")
+    if workspace is None or workspace.nbytes < n.value:
+        workspace = Workspace(int(n.value), x.device)
+    shape = list(x.shape)
+    shape[axis] = k
+    values = torch.empty(shape, dtype=x.dtype, device=x.device)
+    indices = torch.empty(shape, dtype=torch.int64 if index_dtype == I64 else torch.int32, device=x.device)
+    check(lib().vkop_cuda_topk_axis(C.byref(desc), x.data_ptr(), values.data_ptr(), indices.data_ptr(), workspace.ptr,
+                                    workspace.buf.numel(), _stream()), "topk_axis")
     return values, indices
 
 

@@ -181,6 +181,93 @@ int vkop_cuda_topk(const vkop_softmax_topk_desc *desc, const void *input, void *
     return run_select(d, input, out_values, out_indices, nullptr, workspace, workspace_bytes, 0, stream);
 }
 
+// The last-axis selection behind vkop_cuda_topk_axis: rows = outer * inner, raw values, 32-bit indices.
+static int topk_axis_select_desc(const vkop_topk_axis_desc *a, vkop_softmax_topk_desc *d) {
+    if (!a)
+        return VKOP_INVALID_ARG;
+    if (a->outer < 0 || a->inner < 0 || a->axis_len < 1 || a->axis_len > 0x7FFFFFFFll)
+        return VKOP_INVALID_ARG;
+    if (a->outer > 0 && a->inner > 0x7FFFFFFFll / a->outer)
+        return VKOP_UNSUPPORTED;
+    *d = vkop_softmax_topk_desc{};
+    d->rows = a->outer * a->inner;
+    d->cols = a->axis_len;
+    d->dtype = a->dtype;
+    d->k = a->k;
+    d->index_dtype = VKOP_I32;
+    d->value_kind = VKOP_VALUE_RAW;
+    d->inv_temperature = 1.0f;
+    d->largest = a->largest ? 1 : 0;
+    d->path = a->path;
+    if (a->index_dtype != VKOP_I32 && a->index_dtype != VKOP_I64)
+        return VKOP_INVALID_ARG;
+    return validate_select(d, false, nullptr, false, nullptr, nullptr);
+}
+
+int vkop_cuda_topk_axis_workspace(const vkop_topk_axis_desc *desc, size_t *bytes) {
+    if (!bytes)
+        return VKOP_INVALID_ARG;
+    vkop_softmax_topk_desc d;
+    int rc = topk_axis_select_desc(desc, &d);
+    if (rc != VKOP_OK)
+        return rc;
+    SelectPlan plan;
+    rc = plan_select(d, nullptr, &plan);
+    if (rc != VKOP_OK)
+        return rc;
+    *bytes = topk_axis_transposed_bytes(*desc) + topk_axis_values_bytes(*desc) + topk_axis_indices_bytes(*desc) +
+             (plan.bytes + 255) / 256 * 256;
+    return VKOP_OK;
+}
+
+int vkop_cuda_topk_axis(const vkop_topk_axis_desc *desc, const void *input, void *out_values, void *out_indices,
+                        void *workspace, size_t workspace_bytes, void *stream) {
+    vkop_softmax_topk_desc d;
+    int rc = topk_axis_select_desc(desc, &d);
+    if (rc != VKOP_OK)
+        return rc;
+    if (d.rows == 0)
+        return VKOP_OK;
+    if (!input || !out_values || !out_indices)
+        return VKOP_INVALID_ARG;
+    const size_t esz = d.dtype == VKOP_F32 ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(input) % esz != 0 || reinterpret_cast<uintptr_t>(out_values) % esz != 0 ||
+        reinterpret_cast<uintptr_t>(out_indices) % (desc->index_dtype == VKOP_I64 ? 8 : 4) != 0)
+        return VKOP_INVALID_ARG;
+    size_t need = 0;
+    rc = vkop_cuda_topk_axis_workspace(desc, &need);
+    if (rc != VKOP_OK)
+        return rc;
+    if (!workspace || workspace_bytes < need)
+        return VKOP_WORKSPACE_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return VKOP_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char *turned = static_cast<char *>(workspace);
+    char *vals = turned + topk_axis_transposed_bytes(*desc);
+    char *idx = vals + topk_axis_values_bytes(*desc);
+    char *select_ws = idx + topk_axis_indices_bytes(*desc);
+    const size_t select_bytes = need - static_cast<size_t>(select_ws - turned);
+    const void *rows_in = input;
+    if (desc->inner > 1) {
+        rc = launch_transpose_axis(*desc, input, turned, s);
+        if (rc != VKOP_OK)
+            return rc;
+        rows_in = turned;
+    }
+    // the scratch sizes were planned for an aligned input; the turned copy is, the caller's tensor may not be
+    SelectPlan plan;
+    rc = plan_select(d, rows_in, &plan);
+    if (rc != VKOP_OK)
+        return rc;
+    if (plan.bytes > select_bytes)
+        return VKOP_WORKSPACE_TOO_SMALL;
+    rc = run_select(d, rows_in, vals, idx, nullptr, select_ws, select_bytes, 0, stream);
+    if (rc != VKOP_OK)
+        return rc;
+    return launch_place_results(*desc, vals, idx, out_values, out_indices, s);
+}
+
 size_t vkop_cuda_packet_bytes(int32_t k) { return k > 0 ? static_cast<size_t>(packet_words(k)) * 4 : 0; }
 
 int vkop_cuda_softmax_topk_partial(const vkop_softmax_topk_desc *desc, const void *logits_shard, void *packets_out,

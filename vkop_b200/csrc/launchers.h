@@ -77,6 +77,15 @@ struct SelectPlan {
 int launch_softmax(const vkop_softmax_desc &d, const void *input, void *output, cudaStream_t stream);
 
 // ---- NMS (nms.cu) ----
+// TopK along any axis: scratch sizes (256-byte multiples), the axis-to-last transpose and the kernel that
+// puts the selected rows into the [outer, k, inner] output (in ascending index order when sorted == 0).
+size_t topk_axis_transposed_bytes(const vkop_topk_axis_desc &d);
+size_t topk_axis_values_bytes(const vkop_topk_axis_desc &d);
+size_t topk_axis_indices_bytes(const vkop_topk_axis_desc &d);
+int launch_transpose_axis(const vkop_topk_axis_desc &d, const void *in, void *out, cudaStream_t stream);
+int launch_place_results(const vkop_topk_axis_desc &d, const void *vals, const void *idx, void *out_values, void *out_indices,
+                         cudaStream_t stream);
+
 int plan_nms(const vkop_nms_desc &d, size_t *bytes);
 // Strides 0: dense [B, N, 4] boxes and [B, C, N] scores.  Otherwise: elements between the score blocks /
 // the boxes of consecutive batches, and between the four coordinate planes of a box.

@@ -7,7 +7,10 @@
 // Differences from the reference, all widenings: k may be up to 4096 (the
 // reference asserts k < 256, :103), k is not rounded up to even for fp16
 // (:104-106), equal values are ordered by index (the reference's bitonic
-// network leaves them in network order).  The axis must be the last one.
+// network leaves them in network order), any axis 0 .. 2 of the tensor is
+// selected along (the reference's shader always walks the last axis of a 1-D
+// or 2-D tensor, shaders/topk.comp:119-175), and sorted = 0 gives the k entries
+// in ascending index order (the reference ignores the attribute).
 #ifndef VKOP_HOST_OPS_TOPK_HPP_
 #define VKOP_HOST_OPS_TOPK_HPP_
 
@@ -68,19 +71,45 @@ class Topk : public Operator {
             throw std::invalid_argument("TopK: needs a values and an indices output");
         if (outputs[1]->dtype() != typeid(int) && outputs[1]->dtype() != typeid(int64_t))
             throw std::invalid_argument("TopK: indices must be int or int64_t");
-        std::vector<int> out_shape;
-        vkop_softmax_topk_desc d = describe(inputs[0], outputs[1], &out_shape);
+        const auto shape = inputs[0]->getShape();
+        const int rank = inputs[0]->num_dims();
+        const int axis = axis_ < 0 ? axis_ + rank : axis_;
+        if (axis < 0 || axis > 2 || axis >= rank)
+            throw std::invalid_argument("TopK: axis out of range");  // the reference asserts axis <= 2
+        vkop_topk_axis_desc d = {};
+        d.outer = 1;
+        d.inner = 1;
+        for (int i = 0; i < axis; i++)
+            d.outer *= shape[i];
+        for (int i = axis + 1; i < rank; i++)
+            d.inner *= shape[i];
+        d.axis_len = shape[axis];
+        d.dtype = value_dtype(inputs[0]);
+        d.k = k_;
+        d.index_dtype = outputs[1]->dtype() == typeid(int64_t) ? VKOP_I64 : VKOP_I32;
+        d.largest = largest_;
+        d.sorted = sorted_;
+        d.path = VKOP_PATH_AUTO;
+        std::vector<int> out_shape = shape;
+        out_shape[axis] = k_;
         resize_if_empty(outputs[0], out_shape);
         resize_if_empty(outputs[1], out_shape);
         if (outputs[0]->dtype() != inputs[0]->dtype())
             throw std::invalid_argument("TopK: values must have the input's element type");
-        if (outputs[0]->num_elements() < d.rows * d.k || outputs[1]->num_elements() < d.rows * d.k)
+        const int64_t produced = d.outer * d.inner * d.k;
+        if (outputs[0]->num_elements() < produced || outputs[1]->num_elements() < produced)
             throw std::invalid_argument("TopK: output tensors are too small");
         size_t need = 0;
-        check(vkop_cuda_softmax_topk_workspace(&d, &need), "vkop_cuda_softmax_topk_workspace");
-        void *ws = workspace(need, shape_key(d));
-        check(vkop_cuda_topk(&d, device_of(inputs[0]), device_of(outputs[0]), device_of(outputs[1]), ws, workspace_bytes(), stream()),
-              "vkop_cuda_topk");
+        check(vkop_cuda_topk_axis_workspace(&d, &need), "vkop_cuda_topk_axis_workspace");
+        uint64_t key = 1469598103934665603ull;
+        for (uint64_t v : {static_cast<uint64_t>(d.outer), static_cast<uint64_t>(d.axis_len), static_cast<uint64_t>(d.inner),
+                           static_cast<uint64_t>(d.dtype), static_cast<uint64_t>(d.k), static_cast<uint64_t>(d.largest)})
+            key = (key ^ v) * 1099511628211ull;
+        key &= ~1ull;  // the selection descriptors of the fused operator hash to odd keys
+        void *ws = workspace(need, key);
+        check(vkop_cuda_topk_axis(&d, device_of(inputs[0]), device_of(outputs[0]), device_of(outputs[1]), ws, workspace_bytes(),
+                                  stream()),
+              "vkop_cuda_topk_axis");
     }
 
     int k_ = 1, axis_ = -1, largest_ = 1, sorted_ = 1;
