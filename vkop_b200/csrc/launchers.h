@@ -30,6 +30,7 @@ struct StreamPlan {
     int grid;
     int64_t per_cta, nvv, vstride;
     int maxparts, list_cap, parts_per_row, aligned, cluster, threads;
+    int deep;  // whole rows of overlapping calls: smaller tiles, more of them in flight
     size_t counters_bytes, lists_bytes, smem_bytes;
 };
 // base_aligned: the logits pointer is a multiple of 16 (rows then are too when the row stride is)

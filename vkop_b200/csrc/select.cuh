@@ -10,6 +10,33 @@
 
 namespace vkop_cuda {
 
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // every poll loop gives up after about a second
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits (bounded, about a second) until a row's counter of finished calls satisfies the test:
+// exact: it shows `want`; otherwise: it has reached `want`.  The calls it waits for were launched
+// before this one, have all their CTAs running (a call is let in only after every CTA of its
+// predecessor has started) and never wait for a later call.  Called by one thread.
+static __device__ __noinline__ bool wait_row_counter(const unsigned int *row_done, uint32_t want, bool exact) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++) {
+            unsigned int dn;
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done) : "memory");
+            if (exact ? dn == want : static_cast<int>(dn - want) >= 0)
+                return true;
+            __nanosleep(64);
+        }
+        if (global_ns() - t0 > kWaitLimitNs)
+            return false;
+    }
+}
+
 constexpr int kCandCap = 2048;        // candidate slots of the chunk filter
 constexpr int kChunkMaxK = 128;       // largest k served by the chunk path
 constexpr int kMergeMaxSlots = 4096;  // candidates one row may gather for its selection

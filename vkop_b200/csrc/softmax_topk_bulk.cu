@@ -38,7 +38,6 @@
 // and VKOP_TIMEOUT in the workspace status word; the CTA stops issuing copies, walks on without
 // data so that its warps still meet at their barriers, waits (bounded) for the copies in flight and
 // returns.
-#include <cstdlib>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -69,7 +68,6 @@ constexpr int kBulkSets = 4;                        // sets of scratch pools tha
 constexpr int kSelThreads = 256;                    // threads of a selecting CTA
 constexpr int kSelCap = 1024;                       // candidates a row may gather before the exact fallback takes over
 constexpr int kBar = 1;                             // named barrier of the consumer threads
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 static_assert(kBulkJ >= 1 && kBulkJ <= 8 && kBulkJ * kBulkConsumers == kBulkTileVecs, "every consumer thread takes the same share of a tile");
 
 // ---- mbarrier / bulk copy wrappers (shared-memory addresses as 32-bit) ----
@@ -106,11 +104,6 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
 }
 // Waits for the phase with the given parity; false when the limit ran out (then *abort is set) or
 // somebody else has given up.
@@ -205,24 +198,6 @@ __device__ __forceinline__ uint32_t posted_bound(const uint32_t *posted) {
         t = v < t ? v : t;
     }
     return t;
-}
-
-// Waits (bounded, about a second) until the row's counter of finished calls satisfies the test:
-// exact: it shows `want`; otherwise: it has reached `want`.  The calls it waits for were launched
-// before this one and never wait for it.  Called by one thread.
-__device__ __noinline__ bool wait_row_counter(const unsigned int *row_done, uint32_t want, bool exact) {
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-        for (int i = 0; i < 64; i++) {
-            unsigned int dn;
-            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done) : "memory");
-            if (exact ? dn == want : static_cast<int>(dn - want) >= 0)
-                return true;
-            __nanosleep(64);
-        }
-        if (global_ns() - t0 > kWaitLimitNs)
-            return false;
-    }
 }
 
 // ---------------------------------------------------------------------------

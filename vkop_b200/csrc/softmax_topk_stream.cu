@@ -4,9 +4,10 @@
 // tensor: a whole row, one of a few equal parts of a row, or (with more rows than CTA slots) a
 // byte-balanced range that may run across rows, its boundaries snapped to multiples of 256 vectors
 // inside a row so that no CTA holds a sliver.  A CTA walks its range in tiles that are staged
-// through shared memory with cp.async, two stages deep: the copy of the next tile is in flight
-// while the current one is processed, every thread copies into and reads back its own slots only,
-// and the only wait is the hardware wait on the thread's own copy groups (no spin-wait anywhere).
+// through shared memory with cp.async, two stages deep (four stages of half-size tiles for whole rows of
+// 16-bit logits in overlapping calls): the copies of the next tiles are in flight while the current one is
+// processed, every thread copies into and reads back its own slots only, and the only wait of the
+// streaming loop is the hardware wait on the thread's own copy groups.
 //
 // Per tile and thread: the maximum of its elements updates a running maximum m_t and rescales a
 // running exp-sum s_t (online softmax).  The running thread maxima give the selection threshold T
@@ -30,8 +31,10 @@
 // the first read).  With the flag the logits need no ordering, and what remains is: scratch lists
 // alternate between two sets by call parity, so a call only needs the call before its predecessor
 // to be done with a row's lists; and results of one row are written in call order.  Both are
-// checked with one acquire load of a per-row counter of finished calls; only when the check fails
-// does the CTA fall back to griddepcontrol.wait for the whole previous call.  Calls number
+// checked with one acquire load of a per-row counter of finished calls.  When the check fails, a CTA
+// that holds a whole row polls that counter (bounded: the CTA it waits for belongs to an earlier call,
+// is running, and never waits for a later call; measured, such a CTA is a few microseconds behind) and
+// any other CTA, or a poll that ran out, falls back to griddepcontrol.wait for the whole previous call.  Calls number
 // themselves on the device (a call counter advanced by the last CTA to arrive, before the successor is let in), so a
 // replayed CUDA graph needs no changing parameter.  Back-to-back calls then overlap several deep.
 #include "common.cuh"
@@ -44,6 +47,8 @@ namespace vkop_cuda {
 constexpr int kStreamThreads = 512;      // one call at a time: two CTAs per SM
 constexpr int kStreamThreadsSmall = 256; // calls that overlap: four lighter CTAs per SM hide each other's row ends
 constexpr int kStreamVecs = 4;
+constexpr int kStreamDeepVecs = 2;    // whole rows in overlapping calls: smaller tiles ...
+constexpr int kStreamDeepStages = 4;  // ... and more of them in flight
 constexpr int kStreamCtasPerSm = 2;
 constexpr int kNumSms = 148;
 constexpr int kStreamSlots = 4;       // private candidate slots of one thread
@@ -142,7 +147,7 @@ struct PartEnd {
     uint64_t *slot;       // this thread's next private slot (tells how many it filled)
     int c_row, c_v0, c_nvt, part_v0, head, nvr;
     const uint4 *vbase;
-    int stage;            // tile stage that may hold a copy in flight
+    int stage;            // tile stage just consumed (the others may hold copies in flight)
     uint32_t epoch;       // number of this call on its workspace
     bool has_next, waited;
 };
@@ -158,7 +163,7 @@ struct StreamShared {
 // last part to arrive).  Returns whether the CTA has waited for the previous call by now.
 // Kept out of line on purpose: inlined, its many live values cost the streaming loop registers
 // (the loop spills and runs a third slower).
-template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER>
+template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER, int STAGES>
 __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const PartEnd e, const StreamShared sh, uint64_t *s_dyn) {
     constexpr int EPV = Elem<T>::kPerVec;
     constexpr int NW = THREADS / 32;
@@ -166,7 +171,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     constexpr int CAP = kStreamSlots * THREADS;
     constexpr int SLOTS = kStreamSlots;
     uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);
-    uint64_t *s_cand = s_dyn + 2 * TV * 2;
+    uint64_t *s_cand = s_dyn + STAGES * TV * 2;
     uint64_t *s_work = s_cand + CAP;
     uint32_t *s_wm0 = sh.wm0;
     float *s_red = sh.red;
@@ -343,6 +348,7 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         cluster.sync();
         if (cluster.block_rank() == 0) {
             // (the tile stages are free: no CTA of a cluster goes on to another row)
+            static_assert(!CLUSTER || STAGES == 2, "the cluster merge splits two tile stages");
             merge_lists<T, THREADS, true>(p, c_row, mylist, 0, static_cast<int>(parts), s_dyn, s_dyn + 2 * TV, s_red, s_int,
                                           s_tmp);
         }
@@ -351,12 +357,11 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         // ---- the part is the row: select among its candidates and write the result.  Results of
         // one row are written in call order; rarely the previous call has not written its own yet:
         // then wait for all of it. ----
-        if (!waited && !s_flag[0]) {  // look once more before giving up
-            if (tid == 0) {
-                unsigned int dn;
-                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done + c_row) : "memory");
-                s_flag[1] = dn == epoch;
-            }
+        if (!waited && !s_flag[0]) {
+            // the previous call's CTA of this row runs a few microseconds ahead: wait for it alone (its
+            // counter), and only if that runs into the limit for the whole previous call
+            if (tid == 0)
+                s_flag[1] = wait_row_counter(row_done + c_row, epoch, true) ? 1 : 0;
             __syncthreads();
             if (!s_flag[1]) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -408,9 +413,9 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 waited = true;
             }
-            // the tile stage just consumed takes the gathered lists (the other stage may hold a copy
+            // the tile stage just consumed takes the gathered lists (the others may hold a copy
             // in flight), the two candidate regions serve the selection: 8 * THREADS slots each
-            uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + (stage ^ 1) * TV);
+            uint64_t *mbuf = reinterpret_cast<uint64_t *>(s_tile + stage * TV);
             merge_lists<T, THREADS>(p, c_row, rowlists, lstride, nparts, mbuf, s_cand, s_red, s_int, s_tmp);
             __syncthreads();
             // the row's result is written and its lists are read
@@ -423,17 +428,18 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     return waited;
 }
 
-template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER>
+template <typename T, int THREADS, int VECS, bool ALIGNED, bool CLUSTER, int STAGES = 2>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_kernel(const ChunkParams p) {
+    constexpr int AHEAD = STAGES - 1;  // tiles in flight while one is processed
     constexpr int EPV = Elem<T>::kPerVec;
     constexpr int NW = THREADS / 32;
     constexpr int TV = THREADS * VECS;  // vectors per tile
     constexpr int CAP = kStreamSlots * THREADS;  // candidate slots of one row part
     extern __shared__ __align__(16) uint64_t s_dyn[];
-    uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);  // two tile stages of TV vectors
+    uint4 *s_tile = reinterpret_cast<uint4 *>(s_dyn);  // STAGES tile stages of TV vectors
     // First region: while a part streams, SLOTS private slots per thread (slot s of thread t at
     // s * THREADS + t), each (float bits << 32 | index in the row); after the part, the dense list.
-    uint64_t *s_cand = s_dyn + 2 * TV * 2;
+    uint64_t *s_cand = s_dyn + STAGES * TV * 2;
     // Second region: while a part streams, the overflow list of threads whose slots are full
     // (s_count entries); after the part, scratch of the in-CTA selection.
     uint64_t *s_work = s_cand + CAP;
@@ -490,13 +496,17 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
     };
 
-    // ---- tile iterator: (row, first vector slot, slots in the tile, last tile of the row part) ----
+    // ---- tile iterators: (row, first vector slot, slots in the tile).  One walks in front and starts the
+    // copies, AHEAD tiles before the other, which processes them. ----
+    auto tile_len = [&](int tv0, int rem) {
+        const int n = TV < static_cast<int>(nvv) - tv0 ? TV : static_cast<int>(nvv) - tv0;
+        return n > rem ? rem : n;
+    };
     int row = static_cast<int>(Vs / nvv);
     int v0 = static_cast<int>(Vs - static_cast<uint32_t>(row) * nvv);
-    int nvt = TV < static_cast<int>(nvv) - v0 ? TV : static_cast<int>(nvv) - v0;
-    if (nvt > remaining)
-        nvt = remaining;
-    bool part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
+    int nvt = tile_len(v0, remaining);
+    bool part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);  // last tile of the row part
+    int i_row = row, i_v0 = v0, i_nvt = nvt, i_rem = remaining, i_stage = 0;  // the tile to copy next
 
     // this thread's first slot of stage 0, as a shared-memory address
     const uint32_t sdst0 = static_cast<uint32_t>(__cvta_generic_to_shared(s_tile + tid));
@@ -531,8 +541,29 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    // Starts the copy of the next tile that has none yet, or commits an empty group when the range is
+    // exhausted: every call is one copy group, so that the wait below always counts the same.
+    auto issue_next = [&]() {
+        if (i_rem > 0) {
+            issue_tile(i_stage, i_row, i_v0, i_nvt);
+            i_rem -= i_nvt;
+            if (i_rem > 0) {
+                i_v0 += i_nvt;
+                if (i_v0 >= static_cast<int>(nvv)) {
+                    i_row++;
+                    i_v0 = 0;
+                }
+                i_nvt = tile_len(i_v0, i_rem);
+            }
+        } else {
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        i_stage = i_stage + 1 == STAGES ? 0 : i_stage + 1;
+    };
     int stage = 0;
-    issue_tile(0, row, v0, nvt);
+#pragma unroll
+    for (int a = 0; a < AHEAD; a++)
+        issue_next();
 
     // ---- the place of this call among the calls that share its workspace (the first tile is on its
     // way meanwhile).  Every CTA reads the workspace's call counter and then draws an arrival ticket;
@@ -605,31 +636,28 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         int head, nvr;
         const uint4 *vbase;
         row_geom(c_row, head, nvr, vbase);
-        // advance the iterator and start the copy of the next tile into the other stage
+        // start the copy AHEAD tiles in front, wait for the current tile, advance the iterator
         remaining -= nvt;
         const bool has_next = remaining > 0;
-        if (has_next) {
-            v0 += nvt;
-            if (v0 >= static_cast<int>(nvv)) {
-                row++;
-                v0 = 0;
-            }
-            nvt = TV < static_cast<int>(nvv) - v0 ? TV : static_cast<int>(nvv) - v0;
-            if (nvt > remaining)
-                nvt = remaining;
-            part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
-            issue_tile(stage ^ 1, row, v0, nvt);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the copy just started
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        issue_next();
+        asm volatile("cp.async.wait_group %0;" ::"n"(AHEAD) : "memory");  // everything but the AHEAD newest groups
         // the current tile: this thread's own slots of the stage
         uint4 d[VECS];
         uint4 *const cur = s_tile + stage * TV + tid;
 #pragma unroll
         for (int j = 0; j < VECS; j++)
             d[j] = cur[j * THREADS];
-        stage ^= 1;
+        const int consumed = stage;
+        stage = stage + 1 == STAGES ? 0 : stage + 1;
+        if (has_next) {
+            v0 += nvt;
+            if (v0 >= static_cast<int>(nvv)) {
+                row++;
+                v0 = 0;
+            }
+            nvt = tile_len(v0, remaining);
+            part_last = (v0 + nvt == static_cast<int>(nvv)) || (nvt == remaining);
+        }
 
         bool edited = false;  // the words differ from what the stage holds
         if (p.negate) {
@@ -756,7 +784,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             e.head = head;
             e.nvr = nvr;
             e.vbase = vbase;
-            e.stage = stage;
+            e.stage = consumed;
             e.epoch = epoch;
             e.has_next = has_next;
             e.waited = waited;
@@ -769,7 +797,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             sh.flag = s_flag;
             sh.sint = s_int;
             sh.count = &s_count;
-            waited = stream_finish_part<T, THREADS, VECS, ALIGNED, CLUSTER>(p, e, sh, s_dyn);
+            waited = stream_finish_part<T, THREADS, VECS, ALIGNED, CLUSTER, STAGES>(p, e, sh, s_dyn);
             if (has_next) {
                 // ---- reset for the next row part ----
                 __syncthreads();  // every thread is done with the candidate regions and the counters
@@ -861,7 +889,14 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     // counters of finished calls sit in the head of the workspace that the streaming kernels share)
     plan->counters_bytes = ((static_cast<size_t>(d.rows) * 2 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
-    plan->smem_bytes = 2 * static_cast<size_t>(threads) * kStreamVecs * 16 + 2 * static_cast<size_t>(kStreamSlots) * threads * 8;
+    // Whole rows of 16-bit logits in overlapping calls: eight-kilobyte tiles, four stages.  Such a CTA is one of a
+    // few hundred that share the memory system, each limited by what it has in flight: three tiles instead of
+    // one, at the same sixteen elements per thread and tile as 32-bit logits have in a sixteen-kilobyte tile
+    // (measured: 8.4 -> 7.0 us a call for fp16; 32-bit logits, eight elements per tile, lose to the loop overhead).
+    plan->deep = (esz == 2 && threads == kStreamThreadsSmall && parts_per_row == 1 && kStreamThreadsSmall != kStreamThreads) ? 1 : 0;
+    const size_t stage_bytes = plan->deep ? static_cast<size_t>(kStreamDeepStages) * threads * kStreamDeepVecs * 16
+                                          : 2 * static_cast<size_t>(threads) * kStreamVecs * 16;
+    plan->smem_bytes = stage_bytes + 2 * static_cast<size_t>(kStreamSlots) * threads * 8;
     return VKOP_OK;
 }
 
@@ -898,6 +933,9 @@ static int launch_stream_t(const ChunkParams &p, const StreamPlan &plan, cudaStr
     if (plan.cluster > 0)
         rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreads, kStreamVecs, ALIGNED, true>, grid, kStreamThreads,
                         plan.smem_bytes, static_cast<unsigned>(plan.cluster), stream, p);
+    else if (plan.deep)
+        rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreadsSmall, kStreamDeepVecs, ALIGNED, false, kStreamDeepStages>, grid,
+                        kStreamThreadsSmall, plan.smem_bytes, 0u, stream, p);
     else if (plan.threads == kStreamThreadsSmall)
         rc = launch_pdl(softmax_topk_stream_kernel<T, kStreamThreadsSmall, kStreamVecs, ALIGNED, false>, grid,
                         kStreamThreadsSmall, plan.smem_bytes, 0u, stream, p);
