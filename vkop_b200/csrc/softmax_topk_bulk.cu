@@ -295,6 +295,7 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
                 *p.arrive_word = 0u;
                 const unsigned int nx = e + 1u;
                 asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(nx) : "memory");
+                __threadfence();  // performed, not just ordered, before this thread lets the next call in
             }
             ctl->epoch = e;
             __threadfence_block();
@@ -601,6 +602,7 @@ __global__ void __launch_bounds__(kSelThreads) bulk_select_kernel(const __grid_c
             *bp.arrive2 = 0u;
             const unsigned int nx = e + 1u;
             asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(bp.epoch2), "r"(nx) : "memory");
+            __threadfence();  // performed, not just ordered, before this thread lets the next call in
         }
         s_epoch = e;
         // the next call's streaming kernel may start: this kernel is small and runs beside it

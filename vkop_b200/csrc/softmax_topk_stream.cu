@@ -582,6 +582,10 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
             *p.arrive_word = 0u;
             const unsigned int n = e + 1u;
             asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(n) : "memory");
+            // The next call reads both words without any other ordering against this call than its start,
+            // and it starts once every CTA here has passed the signal below: the two stores have to be
+            // performed, not just ordered, before this thread signals.
+            __threadfence();
         }
         s_epoch = e;
     }
@@ -628,7 +632,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t epoch = CLUSTER ? 0u : s_epoch;
-
     for (;;) {
         const int c_row = row;
         const int c_v0 = v0, c_nvt = nvt;
