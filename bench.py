@@ -53,6 +53,7 @@ WORKLOADS = {
     "llm_vocab_f16": (64, 128256, torch.float16, 50, 1.25),
     "batched_classifier": (256, 1000, torch.float32, 5, 1.0),
     "sharded_vocab_bf16": (512, 256000, torch.bfloat16, 64, 1.0),
+    "long_row": (1, 16777216, torch.float32, 1024, 1.0),  # one row of 16 Mi logits, k = 1024: the radix-select path
 }
 NBUF = 8
 GATE_CYCLES = 600_000  # about 0.3 ms of device spin in front of a timed region (see timed())
@@ -173,6 +174,8 @@ def make_inputs(name, seed_base, device):
             x = workloads.llm_vocab(seed=seed_base + b, rows=rows, cols=cols, dtype=dtype)
         elif name == "batched_classifier":
             x = workloads.batched_classifier(seed=seed_base + b, rows=rows, cols=cols)
+        elif name == "long_row":
+            x = workloads.long_row(seed=seed_base + b, cols=cols)
         else:
             x = workloads.spiked_normal(rows, cols, 32, 9.0, 1.5, seed_base + b, dtype)
         bufs.append(x)

@@ -212,3 +212,38 @@ def test_aligned_and_unaligned_pointers_share_a_workspace(capi):
     torch.cuda.synchronize()
     util.assert_indices_equal(o[1], wa[1], "unaligned then aligned")
     util.assert_probs_close(o[0], wa[0], torch.float32, "unaligned then aligned")
+
+
+@pytest.mark.parametrize("path_name", ["AUTO", "BULK"])
+def test_many_overlapping_calls_keep_their_pace(capi, path_name):
+    """Forty thousand overlapping calls replayed from a CUDA graph: every call numbers itself on the device from a
+    counter its predecessor advances.  A call that read that counter too early shared its predecessor's number and
+    sat out a bounded wait of a second; no replay may take anywhere near that, and the last result is right."""
+    path = getattr(capi, "PATH_" + path_name)
+    rows, cols, k = 64, 128256, 50
+    g = torch.Generator().manual_seed(91)
+    xs = [torch.randn(rows, cols, generator=g) for _ in range(4)]
+    xg = [x.cuda() for x in xs]
+    d = capi.make_desc(xg[0], k, 1.25, path=path, flags=capi.FLAG_INPUT_READY)
+    ws = capi.Workspace(capi.softmax_topk_workspace_bytes(d))
+    o = (torch.empty((rows, k), device="cuda"), torch.empty((rows, k), dtype=torch.int32, device="cuda"))
+    for x in xg:
+        capi.softmax_topk(x, k, 1.25, workspace=ws, out=o, path=path, flags=capi.FLAG_INPUT_READY)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(256):
+            capi.softmax_topk(xg[i % 4], k, 1.25, workspace=ws, out=o, path=path, flags=capi.FLAG_INPUT_READY)
+    times = []
+    for rep in range(160):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    assert times[-1] < 100.0 and times[-1] < 20 * times[len(times) // 2], (times[len(times) // 2], times[-5:])
+    wv, wi = util.oracle_softmax_topk(xs[3], k, 1.25)
+    util.assert_indices_equal(o[1], wi, "last of many overlapping calls")
+    util.assert_probs_close(o[0], wv, torch.float32, "last of many overlapping calls")
