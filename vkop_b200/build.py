@@ -42,6 +42,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
     hdr_t = _newest_header()
+    # objects compiled with other flags (VKOP_NVCC_DEFINES) are stale whatever their age
+    stamp, flags = os.path.join(OBJ, "flags.txt"), " ".join(NVCC_FLAGS)
+    if not os.path.exists(stamp) or open(stamp).read() != flags:
+        force = True
+    with open(stamp, "w") as f:
+        f.write(flags)
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
