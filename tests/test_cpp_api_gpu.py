@@ -16,7 +16,8 @@ def test_host_library_exports():
     """No GPU needed: the host library loads and exports its flat entry points."""
     assert os.path.exists(HOST_LIB), "build it with `python -m vkop_b200.build`"
     lib = ctypes.CDLL(HOST_LIB)
-    for name in ("vkop_host_pipeline_create", "vkop_host_pipeline_run", "vkop_host_pipeline_destroy", "vkop_host_last_error"):
+    for name in ("vkop_host_pipeline_create", "vkop_host_pipeline_run", "vkop_host_pipeline_destroy", "vkop_host_last_error",
+                 "vkop_host_model_describe", "vkop_host_model_run"):
         assert hasattr(lib, name), name
 
 

@@ -1,8 +1,11 @@
 // Runtime: the post-processing part of the reference's core/runtime.{hpp,cpp}:
 // RegisterPostProcess (runtime.cpp:480-520), Run (:404-458), ReadResult
-// (:460-478), TraceNode (:522-529), GetOutput.  Loading and scheduling a model
-// graph is not part of this path; the tensor a model would produce is bound
-// with BindOutput and stands in for Runtime::GetOutput()'s model output.
+// (:460-478), TraceNode (:522-529), GetInput / GetOutput, and LoadModel
+// (runtime.cpp:33-363) for model files whose nodes are all operators of this
+// path (Softmax, TopK, NonMaxSuppression): the converted tail of a model.  A
+// node of any other type makes LoadModel throw and name it.  Without a model
+// file the tensor a model would produce is bound with BindOutput and stands in
+// for Runtime::GetOutput()'s model output.
 //
 // RegisterPostProcess(SOFTMAX) immediately followed by
 // RegisterPostProcess(TOPK) on the softmax output -- what benchmark/main.cpp:
@@ -27,8 +30,10 @@ class Runtime {
     Runtime(const std::shared_ptr<VulkanCommandPool> &cmdpool, std::string model_path, std::string cache_dir = "");
     ~Runtime();
 
-    // Not on this path: always throws.
+    // Parses model_path (a .vkopbin file), creates the tensors and one operator per node, in the order of
+    // the file's concurrent levels.  Throws std::runtime_error for a node type that is not on this path.
     void LoadModel();
+    std::shared_ptr<ITensor> GetInput(const std::string &name = "") const;
 
     // The tensor that plays the role of the model's output (first one bound is the default).
     void BindOutput(const std::string &name, const std::shared_ptr<ITensor> &tensor);
@@ -54,8 +59,8 @@ class Runtime {
     int precision_ = 0;  // 0: fp32, 1: fp16
     std::shared_ptr<VulkanCommandPool> m_cmdpool_;
     std::string model_path_, cache_dir_;
-    std::unordered_map<std::string, std::shared_ptr<ITensor>> outputs_;
-    std::string first_output_;
+    std::unordered_map<std::string, std::shared_ptr<ITensor>> inputs_, outputs_;
+    std::string first_input_, first_output_;
     std::unordered_map<std::string, std::shared_ptr<ITensor>> real_outputs_;
     std::vector<std::unique_ptr<ops::Operator>> node_ops_;
     std::vector<std::unordered_map<std::string, std::string>> node_attrs_;

@@ -44,10 +44,8 @@ class Operator {
         m_cmdpool_ = cmdpool;
     }
 
-    virtual void setAttribute(const std::unordered_map<std::string, std::string> &attributes) {
-        for (const auto &attr : attributes)
-            std::printf("attribute %s: %s in operator.\n", attr.first.c_str(), attr.second.c_str());
-    }
+    // (The reference's default prints every attribute; the operators of this path all override it.)
+    virtual void setAttribute(const std::unordered_map<std::string, std::string> &) {}
 
     // "[a,b,c]" -> vector (ops/Operator.hpp:87-118)
     template <typename T>

@@ -46,7 +46,7 @@ namespace ops {
     X(SUB, "Sub", nullptr)                                \
     X(TOPK, "TopK", nullptr)                              \
     X(TRANSPOSE, "Transpose", nullptr)                    \
-    X(NMS, "Nms", nullptr)                                \
+    X(NMS, "Nms", "NonMaxSuppression")                              \
     X(GATHER, "Gather", nullptr)                          \
     X(RANGE, "Range", nullptr)                            \
     X(EXPAND, "Expand", nullptr)                          \

@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "core/runtime.hpp"
+#include "model/load.hpp"
 
 using namespace vkop;
 
@@ -108,5 +109,84 @@ int vkop_host_pipeline_run(void *handle, const void *host_logits, void *host_val
 }
 
 void vkop_host_pipeline_destroy(void *handle) { delete static_cast<Pipeline *>(handle); }
+
+// Parses a .vkopbin model file (no device needed) and writes its description, one line per input, output,
+// node, initializer and level, into buf (NUL-terminated, truncated to cap).  Returns the full length, or
+// -1 with vkop_host_last_error() set.
+long vkop_host_model_describe(const char *path, char *buf, size_t cap) {
+    try {
+        const load::VkModel model(path ? path : "");
+        const std::string text = model.describe();
+        if (buf && cap > 0) {
+            const size_t n = text.size() < cap - 1 ? text.size() : cap - 1;
+            std::memcpy(buf, text.data(), n);
+            buf[n] = 0;
+        }
+        return static_cast<long>(text.size());
+    } catch (const std::exception &e) {
+        g_error = e.what();
+        return -1;
+    }
+}
+
+// Loads a .vkopbin model made of this path's operators (Runtime::LoadModel), copies fp32 host data into its
+// first input, runs it and copies up to two of its outputs (in the file's order) back: out_bytes[i] is the
+// capacity on entry and the bytes written on return.  precision: 0 fp32.
+int vkop_host_model_run(int device, const char *path, const float *host_input, size_t input_elements, void *out0,
+                        size_t *out0_bytes, void *out1, size_t *out1_bytes, double *run_ms) {
+    if (!path || !host_input)
+        return VKOP_INVALID_ARG;
+    try {
+        const load::VkModel model(path);
+        auto dev = std::make_shared<VulkanDevice>(device);
+        auto pool = std::make_shared<VulkanCommandPool>(dev);
+        core::Runtime rt(pool, path, 0);
+        rt.LoadModel();
+        auto in = core::as_tensor<float>(rt.GetInput());
+        if (!in || static_cast<size_t>(in->num_elements()) != input_elements) {
+            g_error = "vkop_host_model_run: the first input has another element count";
+            return VKOP_INVALID_ARG;
+        }
+        in->copyToGPU(pool, host_input);
+        const double t = rt.Run();
+        if (run_ms)
+            *run_ms = t;
+        rt.ReadResult();
+        void *dst[2] = {out0, out1};
+        size_t *cap[2] = {out0_bytes, out1_bytes};
+        for (size_t i = 0; i < model.outputs.size() && i < 2; i++) {
+            if (!dst[i] || !cap[i])
+                continue;
+            auto t_out = rt.GetOutput(model.outputs[i].name);
+            size_t bytes = 0;
+            const void *src = nullptr;
+            if (t_out->dtype() == typeid(float)) {
+                auto tt = core::as_tensor<float>(t_out);
+                bytes = static_cast<size_t>(tt->num_elements()) * sizeof(float);
+                src = tt->data();
+            } else if (t_out->dtype() == typeid(int)) {
+                auto tt = core::as_tensor<int>(t_out);
+                bytes = static_cast<size_t>(tt->num_elements()) * sizeof(int);
+                src = tt->data();
+            } else {
+                g_error = "vkop_host_model_run: unsupported output type";
+                return VKOP_UNSUPPORTED;
+            }
+            if (bytes > *cap[i]) {
+                g_error = "vkop_host_model_run: output buffer too small";
+                return VKOP_WORKSPACE_TOO_SMALL;
+            }
+            std::memcpy(dst[i], src, bytes);
+            *cap[i] = bytes;
+        }
+        return VKOP_OK;
+    } catch (const std::invalid_argument &e) {
+        g_error = e.what();
+        return VKOP_INVALID_ARG;
+    } catch (const std::exception &e) {
+        g_error = e.what();
+        return VKOP_CUDA_ERROR;
+    }
+}
 
 }  // extern "C"

@@ -3,6 +3,9 @@
 
 #include <chrono>
 
+#include <cstring>
+
+#include "model/load.hpp"
 #include "ops/OperatorFactory.hpp"
 
 namespace vkop {
@@ -16,8 +19,149 @@ Runtime::Runtime(const std::shared_ptr<VulkanCommandPool> &cmdpool, std::string 
 
 Runtime::~Runtime() = default;
 
+namespace {
+
+// First element of a small integer or float initializer, as the text an attribute holds.
+std::string scalar_text(const load::VkModel &model, const load::Initializer &init) {
+    const uint8_t *p = model.initializer_data(init.name);
+    if (!p || init.byte_size <= 0)
+        throw std::runtime_error("LoadModel: empty initializer " + init.name);
+    if (init.dtype == "int64" && init.byte_size >= 8) {
+        int64_t v;
+        std::memcpy(&v, p, 8);
+        return std::to_string(v);
+    }
+    if (init.dtype == "int32" && init.byte_size >= 4) {
+        int32_t v;
+        std::memcpy(&v, p, 4);
+        return std::to_string(v);
+    }
+    if (init.dtype == "float32" && init.byte_size >= 4) {
+        float v;
+        std::memcpy(&v, p, 4);
+        return std::to_string(v);
+    }
+    throw std::runtime_error("LoadModel: initializer " + init.name + " of type " + init.dtype + " cannot parameterise an operator");
+}
+
+std::vector<int> to_int_dims(const std::vector<uint32_t> &d) { return std::vector<int>(d.begin(), d.end()); }
+
+}  // namespace
+
+// core/runtime.cpp:33-363, for graphs made of this path's operators.  ONNX passes some parameters as
+// inputs (TopK's K; NonMaxSuppression's max_output_boxes_per_class, iou_threshold, score_threshold):
+// such an input, given as an initializer, becomes the attribute of the same meaning, unless the node
+// already carries that attribute.
 void Runtime::LoadModel() {
-    throw std::runtime_error("Runtime::LoadModel: model graphs are outside the post-processing path; bind the logits with BindOutput");
+    const load::VkModel model(model_path_);
+    auto dev = m_cmdpool_->getVulkanDevice();
+    std::unordered_map<std::string, std::shared_ptr<ITensor>> tensor_map;
+    auto make_value_tensor = [&](const std::vector<int> &dims) -> std::shared_ptr<ITensor> {
+        if (precision_ == 1)
+            return dims.empty() ? std::make_shared<Tensor<uint16_t>>(true) : std::make_shared<Tensor<uint16_t>>(dims, true);
+        return dims.empty() ? std::make_shared<Tensor<float>>(true) : std::make_shared<Tensor<float>>(dims, true);
+    };
+    for (const auto &in : model.inputs) {
+        auto t = make_value_tensor(to_int_dims(in.dims));
+        if (inputs_.empty())
+            first_input_ = in.name;
+        inputs_[in.name] = t;
+        tensor_map[in.name] = t;
+    }
+    // node order: the file's levels when they name every node exactly once, else the file's order
+    std::unordered_map<std::string, const load::Node *> by_name;
+    for (const auto &n : model.nodes)
+        by_name[n.name] = &n;
+    std::vector<const load::Node *> order;
+    for (const auto &level : model.concurrent_execution_levels)
+        for (const auto &name : level) {
+            auto it = by_name.find(name);
+            if (it != by_name.end())
+                order.push_back(it->second);
+        }
+    if (order.size() != model.nodes.size()) {
+        order.clear();
+        for (const auto &n : model.nodes)
+            order.push_back(&n);
+    }
+    for (const load::Node *n : order) {
+        const ops::OpType type = ops::convert_opstring_to_enum(n->op_type);
+        const int rank = n->inputs.empty() ? 0 : static_cast<int>(n->inputs[0].dims.size());
+        auto op = type == ops::OpType::UNKNOWN ? nullptr : ops::create_from_type(type, rank <= 2, precision_, false);
+        if (!op)
+            throw std::runtime_error("LoadModel: node '" + n->name + "' of type " + n->op_type +
+                                     " has no operator on the post-processing path");
+        auto attrs = n->attributes;
+        // NonMaxSuppression: the initializer inputs are, in order, max_output_boxes_per_class, iou_threshold and
+        // score_threshold (ONNX inputs 2-4; they follow the single detection-head input as well)
+        static const char *const kNmsParams[] = {"max_output_boxes_per_class", "iou_threshold", "score_threshold"};
+        size_t nms_param = 0;
+        std::vector<std::shared_ptr<ITensor>> ins, outs;
+        for (size_t i = 0; i < n->inputs.size(); i++) {
+            const std::string &name = n->inputs[i].name;
+            auto tm = tensor_map.find(name);
+            if (tm != tensor_map.end()) {
+                ins.push_back(tm->second);
+                continue;
+            }
+            auto init = model.initializers.find(name);
+            if (init == model.initializers.end())
+                throw std::runtime_error("LoadModel: input '" + name + "' of node '" + n->name + "' is produced by nothing");
+            const char *as_attr = nullptr;
+            if (type == ops::OpType::TOPK && i == 1)
+                as_attr = attrs.count("K") ? "K" : "k";
+            else if (type == ops::OpType::NMS && nms_param < 3)
+                as_attr = kNmsParams[nms_param++];
+            if (as_attr) {
+                if (!attrs.count(as_attr))
+                    attrs[as_attr] = scalar_text(model, init->second);
+                continue;
+            }
+            if (init->second.dtype != "float32")
+                throw std::runtime_error("LoadModel: tensor initializer '" + name + "' must be float32");
+            auto t = std::make_shared<Tensor<float>>(to_int_dims(init->second.dims), true);
+            if (static_cast<int64_t>(t->num_elements()) * 4 != init->second.byte_size)
+                throw std::runtime_error("LoadModel: initializer '" + name + "' has the wrong size");
+            t->copyToGPU(m_cmdpool_, reinterpret_cast<const float *>(model.initializer_data(name)));
+            tensor_map[name] = t;
+            ins.push_back(t);
+        }
+        for (size_t i = 0; i < n->outputs.size(); i++) {
+            std::shared_ptr<ITensor> t;
+            const bool integer = (type == ops::OpType::TOPK && i == 1) || type == ops::OpType::NMS;
+            if (integer)
+                t = std::make_shared<Tensor<int>>(true);
+            else
+                t = make_value_tensor({});
+            tensor_map[n->outputs[i].name] = t;
+            outs.push_back(t);
+        }
+        op->set_name(n->name);
+        op->set_runtime_device(dev, m_cmdpool_);
+        op->setAttribute(attrs);
+        node_ops_.push_back(std::move(op));
+        node_attrs_.push_back(attrs);
+        node_input_tensors_.push_back(ins);
+        node_output_tensors_.push_back(outs);
+    }
+    real_outputs_.clear();
+    for (const auto &o : model.outputs) {
+        auto tm = tensor_map.find(o.name);
+        if (tm == tensor_map.end())
+            throw std::runtime_error("LoadModel: output '" + o.name + "' is produced by no node");
+        if (outputs_.empty())
+            first_output_ = o.name;
+        outputs_[o.name] = tm->second;
+        real_outputs_[o.name] = tm->second;
+    }
+    planned_ = false;
+}
+
+std::shared_ptr<ITensor> Runtime::GetInput(const std::string &name) const {
+    if (inputs_.empty())
+        return nullptr;
+    auto it = inputs_.find(name.empty() ? first_input_ : name);
+    return it == inputs_.end() ? nullptr : it->second;
 }
 
 void Runtime::BindOutput(const std::string &name, const std::shared_ptr<ITensor> &tensor) {

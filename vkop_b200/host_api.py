@@ -15,7 +15,8 @@ import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB_PATH = os.path.join(HERE, "libvkop_host.so")
-EXPORTS = ("vkop_host_pipeline_create", "vkop_host_pipeline_run", "vkop_host_pipeline_destroy", "vkop_host_last_error")
+EXPORTS = ("vkop_host_pipeline_create", "vkop_host_pipeline_run", "vkop_host_pipeline_destroy", "vkop_host_last_error",
+           "vkop_host_model_describe", "vkop_host_model_run")
 
 _lib = None
 
