@@ -63,7 +63,11 @@ typedef enum vkop_select_path {
  * operation of the same stream still writes them.  The kernel may then start
  * reading them while the previous kernel of the stream is still draining
  * (programmatic dependent launch); its own writes still wait for that kernel.
- * Leave it clear when the logits come from the kernel just before. */
+ * Leave it clear when the logits come from the kernel just before.
+ * Calls with the flag number themselves in their workspace and order their
+ * result rows by that number: between two of them that share a workspace or an
+ * output buffer, enqueue no other kernel that writes those outputs, and let
+ * every output buffer written by overlapping calls belong to one workspace. */
 #define VKOP_FLAG_INPUT_READY 1
 
 /* Library version (VKOP_CUDA_VERSION of the build). */
@@ -191,7 +195,9 @@ int vkop_cuda_sample_topk(const void *values, int32_t dtype, const void *indices
  * `slots` of 2 * world * packets_bytes bytes and `flags` of 2 * world uint32,
  * both zeroed once and mapped into every peer's address space (CUDA IPC or
  * symmetric memory; peer access enabled).  Step `seq` (1, 2, 3, ... on every
- * rank alike) uses half seq & 1 of both.
+ * rank alike) uses half seq & 1 of both.  seq is never 0 (the cleared flags read
+ * as 0) and differs from the previous step's in its lowest bit: a 32-bit counter
+ * that wraps must skip 0 and keep alternating.
  *
  * vkop_cuda_packets_push stores this rank's packets (the output of `partial`)
  * into slot [seq & 1][rank] of every rank's buffer -- peer_slots / peer_flags

@@ -11,6 +11,8 @@ Two ways to shard (the reference runs on a single device; both are extensions of
 """
 from __future__ import annotations
 
+import ctypes as _ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -30,9 +32,6 @@ def exchange_packets(packets: torch.Tensor, group=None, out: torch.Tensor | None
     # the flat [world * rows, words] view is the form every backend accepts
     dist.all_gather_into_tensor(out.view(world * packets.shape[0], *packets.shape[1:]), packets.contiguous(), group=group)
     return out
-
-
-import ctypes as _ctypes
 
 
 class _IpcHandle(_ctypes.Structure):
@@ -161,12 +160,10 @@ class VocabShardedSoftmaxTopk:
         self.gathered = torch.empty((self.world, rows, words), dtype=torch.int32, device=dev)
         self.values = torch.empty((rows, k), dtype=dtype, device=dev)
         self.indices = torch.empty((rows, k), dtype=torch.int64 if index_dtype == capi.I64 else torch.int32, device=dev)
-        probe = torch.empty((rows, shard_cols), dtype=dtype, device="meta")
         desc = capi.SoftmaxTopkDesc(rows=rows, cols=shard_cols, row_stride=shard_cols, dtype=capi._TORCH_DTYPE[dtype], k=k,
                                     index_dtype=index_dtype, value_kind=capi.VALUE_PROBABILITY,
                                     inv_temperature=inv_temperature, largest=1, path=0, splits=0,
                                     index_offset=index_offset)
-        del probe
         self.workspace = capi.Workspace(capi.softmax_topk_workspace_bytes(desc), dev)
         self.peer = PeerPacketExchange(rows, words, group, dev) if (exchange == "peer" and self.world > 1) else None
 
