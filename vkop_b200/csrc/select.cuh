@@ -5,6 +5,7 @@
 #pragma once
 
 #include <cooperative_groups.h>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -22,12 +23,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // exact: it shows `want`; otherwise: it has reached `want`.  The calls it waits for were launched
 // before this one, have all their CTAs running (a call is let in only after every CTA of its
 // predecessor has started) and never wait for a later call.  Called by one thread.
-static __device__ __noinline__ bool wait_row_counter(const unsigned int *row_done, uint32_t want, bool exact) {
+static __device__ __noinline__ bool wait_row_counter(const unsigned int *row_done, uint32_t want, bool exact,
+                                                     uint32_t mask = 0xFFFFFFFFu) {
     const unsigned long long t0 = global_ns();
+    want &= mask;
     for (;;) {
         for (int i = 0; i < 64; i++) {
             unsigned int dn;
             asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(dn) : "l"(row_done) : "memory");
+            dn &= mask;
             if (exact ? dn == want : static_cast<int>(dn - want) >= 0)
                 return true;
             __nanosleep(64);
@@ -73,10 +77,64 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// Results of one row reach the outputs in call order, and no CTA holds its place on an SM waiting for
+// that.  A row has an order word: the number of calls that have finished the row (low 16 bits) and one
+// bit per call that has deposited its result (bit 16 + call % 16), and a mailbox of kMailSlots entries
+// (entry = the two addresses the result belongs at, then the k values and the k indices exactly as
+// they would have been stored).  A CTA that has ranked its row and finds that the previous call has
+// not finished the row yet writes its result into entry call % 16, sets its bit and leaves.  A CTA
+// that finds it is its turn writes straight to the outputs, then delivers the entries that later calls
+// have deposited meanwhile, in call order, and publishes the new count with a compare-and-swap that
+// fails whenever a bit has appeared in between (row_order_finish).  A depositor whose bit lands after
+// the count already names it delivers its own entry.  Either way the outputs receive the calls'
+// results in call order.  Since a deposited result is delivered by a CTA of an earlier kernel, CTA 0 of
+// every kernel waits for its predecessor kernel before it ends: a kernel has then completed only when
+// every earlier one has.  Without a mailbox (packets as output), or when the entry is still taken,
+// the CTA waits for its turn instead (bounded poll of the word, then the whole previous kernel).
+constexpr int kMailSlots = 16;
+struct OrderWait {
+    unsigned int *word;   // the row's order word
+    uint32_t epoch;       // number of this call
+    int *flag;            // a word of shared memory
+    unsigned char *mail;  // the row's mailbox (null: none)
+    uint32_t mail_stride, mail_idx_off;  // bytes per entry; offset of the indices in an entry
+    bool need;            // the previous call had not finished the row when this CTA last looked
+    bool waited;          // in/out: this thread has waited for the whole previous kernel
+    bool deposited;       // out: the result belongs in the mailbox entry, not at the outputs
+};
+__device__ __forceinline__ uint32_t mail_bit(uint32_t call) { return 0x10000u << (call & (kMailSlots - 1)); }
+
+// Called by every thread of the selecting CTA right before its first store.
+template <int BAR, int THREADS>
+__device__ __forceinline__ void order_hook(OrderWait *ow) {
+    if (ow == nullptr || !ow->need || ow->waited)
+        return;
+    if (threadIdx.x == 0) {
+        unsigned int w;
+        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(w) : "l"(ow->word) : "memory");
+        int f;
+        if (((w ^ ow->epoch) & 0xFFFFu) == 0u)
+            f = 1;  // its turn by now
+        else if (ow->mail != nullptr && (w & mail_bit(ow->epoch)) == 0u && ((ow->epoch - w) & 0xFFFFu) < kMailSlots)
+            f = 2;  // deposit (fewer than kMailSlots calls of the row are unfinished: nobody else has or takes this entry)
+        else
+            f = wait_row_counter(ow->word, ow->epoch, true, 0xFFFFu) ? 1 : 0;
+        *ow->flag = f;
+    }
+    cta_sync<BAR, THREADS>();
+    const int f = *ow->flag;
+    if (f == 0) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        ow->waited = true;
+    }
+    ow->deposited = f == 2;
+    ow->need = false;
+}
+
 // Where a ranked survivor goes: the final outputs, a packet, or a candidate list.
 template <typename T>
 __device__ __forceinline__ void emit(const ChunkParams &p, int64_t row, int rank, uint64_t comp, float m, float s,
-                                     unsigned long long *list_out) {
+                                     unsigned long long *list_out, const OrderWait *ow = nullptr) {
     if (list_out) {
         list_out[rank] = comp;
         return;
@@ -88,14 +146,89 @@ __device__ __forceinline__ void emit(const ChunkParams &p, int64_t row, int rank
         pk[4 + p.k + rank] = idx + static_cast<uint32_t>(p.index_offset);
         return;
     }
-    const int64_t o = row * p.k + rank;
+    // (a result that has to wait for its turn goes to the row's mailbox entry in the same form)
+    const bool mailed = ow != nullptr && ow->deposited;
+    unsigned char *const entry = mailed ? ow->mail + (ow->epoch & (kMailSlots - 1)) * ow->mail_stride : nullptr;
+    void *const ov = mailed ? static_cast<void *>(entry + 16) : p.out_values;
+    void *const oi = mailed ? static_cast<void *>(entry + ow->mail_idx_off) : p.out_indices;
+    const int64_t o = mailed ? rank : row * p.k + rank;
     if (p.value_kind == VKOP_VALUE_RAW) {
-        reinterpret_cast<T *>(p.out_values)[o] = reinterpret_cast<const T *>(p.logits)[row * p.row_stride + idx];
+        reinterpret_cast<T *>(ov)[o] = reinterpret_cast<const T *>(p.logits)[row * p.row_stride + idx];
     } else {
-        store_value<T>(p.out_values, o, softmax_prob(key_to_float(cand_key(comp)), p.inv_t, m, s));
+        store_value<T>(ov, o, softmax_prob(key_to_float(cand_key(comp)), p.inv_t, m, s));
     }
-    store_index(p.out_indices, p.index_dtype, o, static_cast<int64_t>(idx) + p.index_offset);
+    store_index(oi, p.index_dtype, o, static_cast<int64_t>(idx) + p.index_offset);
 }
+
+// Copies a mailbox entry to the addresses in its header.  Executed by one warp.
+template <typename T>
+__device__ __forceinline__ void deliver_entry(const unsigned char *entry, uint32_t idx_off, int k, int index_dtype) {
+    const int lane = threadIdx.x & 31;
+    // (the entry was written by another SM: read it from the L2)
+    const unsigned long long h0 = __ldcg(reinterpret_cast<const unsigned long long *>(entry));
+    const unsigned long long h1 = __ldcg(reinterpret_cast<const unsigned long long *>(entry + 8));
+    using Bits = typename std::conditional<sizeof(T) == 4, unsigned int, unsigned short>::type;
+    Bits *const dv = reinterpret_cast<Bits *>(h0);
+    void *const di = reinterpret_cast<void *>(h1);
+    const Bits *const sv = reinterpret_cast<const Bits *>(entry + 16);
+    for (int i = lane; i < k; i += 32) {
+        dv[i] = __ldcg(sv + i);
+        if (index_dtype == VKOP_I64)
+            reinterpret_cast<long long *>(di)[i] = __ldcg(reinterpret_cast<const long long *>(entry + idx_off) + i);
+        else
+            reinterpret_cast<int *>(di)[i] = __ldcg(reinterpret_cast<const int *>(entry + idx_off) + i);
+    }
+}
+
+// After the stores of a row's result (all threads, then a CTA barrier): settles the row's order word.
+// Executed by warp 0 of the CTA.  See OrderWait.
+template <typename T>
+__device__ __noinline__ void row_order_finish(const ChunkParams &p, const OrderWait ow, int64_t row) {
+    const int lane = threadIdx.x & 31;
+    uint32_t cur = ow.epoch, cleared = 0u;
+    if (ow.deposited) {
+        unsigned char *const entry = ow.mail + (cur & (kMailSlots - 1)) * ow.mail_stride;
+        unsigned int old = 0u;
+        if (lane == 0) {
+            const size_t isz = p.index_dtype == VKOP_I64 ? 8 : 4;
+            *reinterpret_cast<void **>(entry) = static_cast<char *>(p.out_values) + row * p.k * sizeof(T);
+            *reinterpret_cast<void **>(entry + 8) = static_cast<char *>(p.out_indices) + row * p.k * isz;
+            __threadfence();  // the entry (written by the whole CTA before the barrier) before the bit
+            asm volatile("atom.acq_rel.gpu.global.or.b32 %0, [%1], %2;" : "=r"(old) : "l"(ow.word), "r"(mail_bit(cur)) : "memory");
+        }
+        old = __shfl_sync(kFullMask, old, 0);
+        if (((old ^ cur) & 0xFFFFu) != 0u)
+            return;  // an earlier call of this row delivers it
+        // the previous call published its count before the bit was there: this CTA delivers its own entry
+        deliver_entry<T>(entry, ow.mail_idx_off, p.k, p.index_dtype);
+        cleared = mail_bit(cur);
+    }
+    // this call's result is in place: deliver what later calls have deposited, in call order, then publish
+    for (int it = 0; it < 256; it++) {
+        unsigned int w = 0u;
+        if (lane == 0)
+            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(w) : "l"(ow.word) : "memory");
+        w = __shfl_sync(kFullMask, w, 0);
+        const uint32_t nb = mail_bit(cur + 1u);
+        if (ow.mail != nullptr && (w & nb) != 0u && (cleared & nb) == 0u) {
+            deliver_entry<T>(ow.mail + ((cur + 1u) & (kMailSlots - 1)) * ow.mail_stride, ow.mail_idx_off, p.k, p.index_dtype);
+            cleared |= nb;
+            cur++;
+            continue;
+        }
+        const uint32_t desired = ((w & 0xFFFF0000u) & ~cleared) | ((cur + 1u) & 0xFFFFu);
+        unsigned int seen = 0u;
+        __threadfence();  // the deliveries of all lanes before the count
+        __syncwarp();
+        if (lane == 0)
+            asm volatile("atom.acq_rel.gpu.global.cas.b32 %0, [%1], %2, %3;" : "=r"(seen) : "l"(ow.word), "r"(w), "r"(desired) : "memory");
+        seen = __shfl_sync(kFullMask, seen, 0);
+        if (seen == w)
+            return;
+    }
+}
+
+
 
 // Warp bitonic sort of one 64-bit value per lane, descending by lane.
 __device__ __forceinline__ uint64_t warp_sort_desc(uint64_t v, int lane) {
@@ -117,10 +250,13 @@ __device__ __forceinline__ uint64_t warp_sort_desc(uint64_t v, int lane) {
 // memory (list[0..n)); `work` is a second region of at least n slots.  The
 // survivors are emitted at their rank.  Executed by THREADS threads (the whole
 // CTA, or with BAR > 0 the threads 0 .. THREADS-1 that share named barrier
-// BAR); list and work are clobbered.
+// BAR); list and work are clobbered.  ow (may be null): an order to keep
+// between overlapping calls; it is waited for as late as possible, after the
+// ranking and right before the first store, so that the stretch a successor
+// may have to wait for is the stores alone.
 template <typename T, int THREADS, int BAR = 0>
 __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, uint64_t *list, int n, uint64_t *work, float M,
-                                float S, unsigned long long *list_out, int *s_tmp) {
+                                float S, unsigned long long *list_out, int *s_tmp, OrderWait *ow = nullptr) {
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = p.k;
@@ -130,6 +266,22 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
     if (n <= kSmall) {
         constexpr int PER = THREADS / kSmall >= 1 ? THREADS / kSmall : 1;
         static_assert(PER <= 32 && (PER & (PER - 1)) == 0, "a power of two within a warp");
+        if constexpr (THREADS / PER >= kSmall) {
+            // every candidate has its threads: count first, wait for the order, then store
+            const int c = tid / PER, sub = tid % PER;
+            const uint64_t me = c < n ? list[c] : ~0ull;
+            int beat = 0;
+            for (int i = sub; i < n; i += PER)
+                beat += list[i] > me ? 1 : 0;
+#pragma unroll
+            for (int o = 1; o < PER; o <<= 1)
+                beat += __shfl_xor_sync(kFullMask, beat, o);
+            order_hook<BAR, THREADS>(ow);
+            if (c < n && sub == 0 && beat < k)
+                emit<T>(p, row, beat, me, M, S, list_out, ow);
+            return;
+        }
+        order_hook<BAR, THREADS>(ow);
         for (int c0 = 0; c0 < kSmall; c0 += THREADS / PER) {
             const int c = c0 + tid / PER, sub = tid % PER;
             const uint64_t me = c < n ? list[c] : ~0ull;
@@ -140,7 +292,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
             for (int o = 1; o < PER; o <<= 1)
                 beat += __shfl_xor_sync(kFullMask, beat, o);
             if (c < n && sub == 0 && beat < k)
-                emit<T>(p, row, beat, me, M, S, list_out);
+                emit<T>(p, row, beat, me, M, S, list_out, ow);
         }
         return;
     }
@@ -199,6 +351,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
         work[i] = v;
     }
     cta_sync<BAR, THREADS>();
+    order_hook<BAR, THREADS>(ow);
     for (int g = warp; g < ng; g += NW) {
         const uint64_t me = work[g * 32 + lane];
         int rank = lane;
@@ -221,7 +374,7 @@ __device__ __noinline__ void select_and_emit(const ChunkParams &p, int64_t row, 
                 rank += lo;
             }
             if (rank < k)
-                emit<T>(p, row, rank, me, M, S, list_out);
+                emit<T>(p, row, rank, me, M, S, list_out, ow);
         }
     }
 }

@@ -230,7 +230,8 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
     if (tid == 0) {
         s_tmp[0] = 0;
         // scratch lists: calls 0 .. epoch - 2 are done with them; whole rows: results come in call order
-        s_flag[0] = whole ? done_calls == epoch : static_cast<int>(done_calls - epoch + 1u) >= 0;
+        // (whole rows: the row's order word, calls finished in its low 16 bits; see OrderWait)
+        s_flag[0] = whole ? ((done_calls ^ epoch) & 0xFFFFu) == 0u : static_cast<int>(done_calls - epoch + 1u) >= 0;
     }
     __syncthreads();
     uint32_t mkey = lane < NW ? s_wm0[lane] : 0u;
@@ -354,20 +355,27 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
         }
         cluster.sync();  // the other CTAs keep their shared memory until it has been read
     } else if (whole) {
-        // ---- the part is the row: select among its candidates and write the result.  Results of
-        // one row are written in call order; rarely the previous call has not written its own yet:
-        // then wait for all of it. ----
-        if (!waited && !s_flag[0]) {
-            // the previous call's CTA of this row runs a few microseconds ahead: wait for it alone (its
-            // counter), and only if that runs into the limit for the whole previous call
-            if (tid == 0)
-                s_flag[1] = wait_row_counter(row_done + c_row, epoch, true) ? 1 : 0;
-            __syncthreads();
-            if (!s_flag[1]) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                waited = true;
-            }
+        // ---- the part is the row: select among its candidates and write the result.  Results of one
+        // row reach the outputs in call order, without this CTA waiting for the previous call's CTA of
+        // the row: when that one has not finished, the result is left in the row's mailbox for it to
+        // deliver (OrderWait, row_order_finish). ----
+        OrderWait ow;
+        ow.word = row_done + c_row;
+        ow.epoch = epoch;
+        ow.flag = &s_flag[1];
+        {
+            const uint32_t vb = (static_cast<uint32_t>(p.k) * sizeof(T) + 15u) & ~15u;
+            const uint32_t ib = (static_cast<uint32_t>(p.k) * (p.index_dtype == VKOP_I64 ? 8u : 4u) + 15u) & ~15u;
+            ow.mail_idx_off = 16u + vb;
+            ow.mail_stride = 16u + vb + ib;
+            ow.mail = p.packets_out ? nullptr
+                                    : reinterpret_cast<unsigned char *>(p.lists) + static_cast<size_t>(c_row) * kMailSlots * ow.mail_stride;
         }
+        ow.need = !waited && !s_flag[0];
+        ow.waited = waited;
+        ow.deposited = false;
+        select_and_emit<T, THREADS>(p, c_row, reinterpret_cast<uint64_t *>(mylist + 2), C, s_dyn, mz, S, nullptr, s_tmp, &ow);
+        waited = ow.waited;
         if (p.packets_out && tid == 0) {
             uint32_t *pk = p.packets_out + static_cast<int64_t>(c_row) * packet_words(p.k);
             pk[0] = __float_as_uint(mz);
@@ -375,12 +383,9 @@ __device__ __noinline__ bool stream_finish_part(const ChunkParams &p, const Part
             pk[2] = static_cast<uint32_t>(C < p.k ? C : p.k);
             pk[3] = 0;
         }
-        select_and_emit<T, THREADS>(p, c_row, reinterpret_cast<uint64_t *>(mylist + 2), C, s_dyn, mz, S, nullptr, s_tmp);
         __syncthreads();
-        if (tid == 0) {
-            const unsigned int d = epoch + 1u;
-            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(row_done + c_row), "r"(d) : "memory");
-        }
+        if (warp == 0)
+            row_order_finish<T>(p, ow, c_row);
     } else {
     // ---- announce the part; the last part of a row to arrive merges the row ----
         if (tid == 0) {
@@ -820,6 +825,10 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         if (!has_next)
             break;
     }
+    // Whole rows in overlapping calls: a result may have been left for a CTA of an earlier kernel to
+    // deliver, so this kernel must not complete before its predecessor has: one CTA waits for it.
+    if (!CLUSTER && parts == 1 && blockIdx.x == 0 && !waited)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -853,7 +862,11 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
         }
         if (d.splits > 0)
             s = d.splits;  // the caller's choice of CTAs per row
-        if (s <= slots && nvv / s >= 2 * kUnit && d.rows * s <= tiles) {
+        // (decided on the slot count of aligned rows whatever the pointer: calls with aligned and
+        // unaligned logits may share a workspace, and the meaning of the rows' order words follows the shape)
+        const int64_t nvv_a = (d.cols + epv - 1) / epv;
+        const int64_t tiles_a = (d.rows * nvv_a + tile - 1) / tile;
+        if (s <= slots && nvv_a / s >= 2 * kUnit && d.rows * s <= tiles_a) {
             parts_per_row = static_cast<int>(s);  // the same number of CTAs for every row: no CTA crosses a row
             grid = d.rows * s;
         }
@@ -892,6 +905,13 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     // counters of finished calls sit in the head of the workspace that the streaming kernels share)
     plan->counters_bytes = ((static_cast<size_t>(d.rows) * 2 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
+    if (overlapping && parts_per_row == 1) {
+        // whole rows publish no lists; the region holds the rows' mailboxes (kMailSlots entries of two
+        // addresses, k values and k indices, each block rounded up to 16 bytes)
+        const size_t entry = 16 + ((static_cast<size_t>(d.k) * esz + 15) & ~static_cast<size_t>(15)) +
+                             ((static_cast<size_t>(d.k) * (d.index_dtype == VKOP_I64 ? 8 : 4) + 15) & ~static_cast<size_t>(15));
+        plan->lists_bytes = static_cast<size_t>(d.rows) * kMailSlots * entry;
+    }
     // Whole rows of 16-bit logits in overlapping calls: eight-kilobyte tiles, four stages.  Such a CTA is one of a
     // few hundred that share the memory system, each limited by what it has in flight: three tiles instead of
     // one, at the same sixteen elements per thread and tile as 32-bit logits have in a sixteen-kilobyte tile
