@@ -321,6 +321,46 @@ def test_stream_overlapping_calls_in_every_launch_shape(capi, rows, cols, k, dty
     util.assert_indices_equal(o[1], want[2][1], f"overlapping, shared output {rows}x{cols}")
 
 
+@pytest.mark.parametrize("dtype,index64,cols", [(torch.float32, False, 128256), (torch.float16, True, 70001)])
+def test_overlapping_whole_row_calls_deliver_in_call_order(capi, dtype, index64, cols):
+    """One CTA per row, several hundred calls in flight one behind the other on one workspace: a call whose
+    predecessor has not finished a row leaves that row's result for the predecessor's CTA to deliver (the row's
+    mailbox).  Two output buffers are written in turn from five inputs; a kernel enqueued right behind the last
+    call (the copies below) must see, in either buffer, the result of the last call that wrote it."""
+    rows, k, calls = 64, 50, 403
+    g = torch.Generator().manual_seed(cols + k)
+    xs = [(torch.randn(rows, cols, generator=g) * 2).to(dtype) for _ in range(5)]
+    xg = [x.cuda() for x in xs]
+    itype = capi.I64 if index64 else capi.I32
+    d = capi.make_desc(xg[0], k, 1.25, itype, path=capi.PATH_STREAM, flags=capi.FLAG_INPUT_READY)
+    ws = capi.Workspace(capi.softmax_topk_workspace_bytes(d))
+    outs = [(torch.zeros((rows, k), dtype=dtype, device="cuda"),
+             torch.zeros((rows, k), dtype=torch.int64 if index64 else torch.int32, device="cuda")) for _ in range(2)]
+
+    def enqueue():
+        for i in range(calls):
+            capi.softmax_topk(xg[i % 5], k, 1.25, index_dtype=itype, workspace=ws, out=outs[i % 2], path=capi.PATH_STREAM,
+                              flags=capi.FLAG_INPUT_READY)
+
+    enqueue()  # (from the host, slower than the device: little overlap)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()  # replayed, the calls run as deep as the GPU has room
+    with torch.cuda.graph(graph):
+        enqueue()
+    for rep in range(4):
+        for o in outs:
+            o[0].zero_()
+            o[1].zero_()
+        graph.replay()
+        seen = [(o[0].clone(), o[1].clone()) for o in outs]  # enqueued behind the last call, no synchronisation
+        torch.cuda.synchronize()
+        for b in range(2):
+            last = max(i for i in range(calls) if i % 2 == b)
+            wv, wi = util.oracle_softmax_topk(xs[last % 5], k, 1.25)
+            util.assert_indices_equal(seen[b][1], wi, f"buffer {b}, round {rep}")
+            util.assert_probs_close(seen[b][0], wv, dtype, f"buffer {b}, round {rep}")
+
+
 def test_stream_raw_smallest_and_packets(capi):
     g = torch.Generator().manual_seed(53)
     x = torch.randn(40, 70001, generator=g)

@@ -68,6 +68,7 @@ struct ChunkParams {
     // calls on one workspace number themselves (streaming kernels): the call counter, the CTAs of the
     // current call that have drawn their arrival ticket, and per row the calls whose result is written
     unsigned int *epoch_word, *arrive_word, *row_done;
+    unsigned int *row_ticket;  // per row: calls started on the row (whole rows in overlapping calls number themselves per row)
 };
 
 

@@ -757,7 +757,8 @@ __global__ void __launch_bounds__(kSelThreads) bulk_select_kernel(const __grid_c
 
 // ---------------------------------------------------------------------------
 
-size_t stream_common_bytes(int64_t rows) { return 256 + ((static_cast<size_t>(rows) * 4 + 255) / 256) * 256; }
+// head (call counters, status) | per row: order word / calls finished | per row: calls started
+size_t stream_common_bytes(int64_t rows) { return 256 + 2 * ((static_cast<size_t>(rows) * 4 + 255) / 256) * 256; }
 
 int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan) {
     if (d.k > kChunkMaxK)

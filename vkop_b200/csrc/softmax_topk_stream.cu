@@ -28,15 +28,22 @@
 // Launches use programmatic stream serialization.  A kernel lets its successor in as soon as all
 // its CTAs run (griddepcontrol.launch_dependents) and orders itself against its predecessor only
 // where memory demands it.  Without VKOP_FLAG_INPUT_READY that is at once (griddepcontrol.wait before
-// the first read).  With the flag the logits need no ordering, and what remains is: scratch lists
-// alternate between two sets by call parity, so a call only needs the call before its predecessor
-// to be done with a row's lists; and results of one row are written in call order.  Both are
-// checked with one acquire load of a per-row counter of finished calls.  When the check fails, a CTA
-// that holds a whole row polls that counter (bounded: the CTA it waits for belongs to an earlier call,
-// is running, and never waits for a later call; measured, such a CTA is a few microseconds behind) and
-// any other CTA, or a poll that ran out, falls back to griddepcontrol.wait for the whole previous call.  Calls number
-// themselves on the device (a call counter advanced by the last CTA to arrive, before the successor is let in), so a
-// replayed CUDA graph needs no changing parameter.  Back-to-back calls then overlap several deep.
+// the first read).  With the flag the logits need no ordering, back-to-back calls overlap several deep,
+// and what remains is the order of the results and of the scratch lists:
+//   whole rows   Calls number themselves per row: the CTA of a row draws a ticket from the row's own
+//                counter, first thing, one round trip before it lets the successor in.  Results of one
+//                row reach the outputs in call order through the row's order word and mailbox (OrderWait
+//                in select.cuh): a CTA whose predecessor has not finished the row leaves its ranked result
+//                for that CTA to deliver and goes; nobody waits holding a place on an SM.  CTA 0 of every
+//                kernel waits for the previous kernel before it ends, so that a kernel has completed only
+//                when all earlier ones have.
+//   otherwise    Calls number themselves in the workspace (a call counter advanced by the last CTA of a
+//                call to arrive, before the successor is let in).  Scratch lists alternate between two sets
+//                by call parity, so a call only needs the call before its predecessor to be done with a
+//                row's lists; and results of one row are written in call order.  Both are checked with one
+//                acquire load of a per-row counter of finished calls; when the check fails the CTA falls
+//                back to griddepcontrol.wait for the whole previous call.
+// A replayed CUDA graph needs no changing parameter either way.
 #include "common.cuh"
 #include "launchers.h"
 #include "select.cuh"
@@ -477,6 +484,12 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         return;
     }
     int remaining = static_cast<int>(Ve - Vs);
+    // Whole rows in overlapping calls: the calls of one row are numbered by a ticket of that row alone,
+    // drawn here, first thing, by one thread (CTA c holds row c).  One round trip, no other CTA involved.
+    const bool row_tickets = !CLUSTER && parts == 1 && p.input_ready;
+    unsigned int ticket = 0;
+    if (row_tickets && tid == 0)
+        asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.row_ticket + blockIdx.x) : "memory");
     bool waited = false;
     if (!p.input_ready) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -579,7 +592,10 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     // right before it, only for those of the call before that.
     // CLUSTER (the CTAs of one row form a thread-block cluster and hand their parts over in shared
     // memory) is used for calls that wait for their predecessor at once: nothing to number. ----
-    if (!CLUSTER && tid == 0) {
+    if (row_tickets) {
+        if (tid == 0)
+            s_epoch = ticket;
+    } else if (!CLUSTER && tid == 0) {
         unsigned int e, t;
         asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(p.epoch_word) : "memory");
         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(p.arrive_word) : "memory");
@@ -995,6 +1011,7 @@ int launch_stream(const vkop_softmax_topk_desc &d, const StreamPlan &plan, const
     p.arrive_word = reinterpret_cast<unsigned int *>(common_ws);
     p.epoch_word = reinterpret_cast<unsigned int *>(static_cast<char *>(common_ws) + 4);
     p.row_done = reinterpret_cast<unsigned int *>(static_cast<char *>(common_ws) + 256);
+    p.row_ticket = p.row_done + ((static_cast<size_t>(d.rows) + 63) / 64) * 64;
     p.counters = reinterpret_cast<unsigned int *>(workspace);
     p.lists = reinterpret_cast<unsigned long long *>(static_cast<char *>(workspace) + plan.counters_bytes);
     p.packets_out = reinterpret_cast<uint32_t *>(packets_out);
