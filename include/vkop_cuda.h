@@ -67,7 +67,10 @@ typedef enum vkop_select_path {
  * Calls with the flag number themselves in their workspace and order their
  * result rows by that number: between two of them that share a workspace or an
  * output buffer, enqueue no other kernel that writes those outputs, and let
- * every output buffer written by overlapping calls belong to one workspace. */
+ * every output buffer written by overlapping calls belong to one workspace.
+ * Results reach the outputs in call order, and the kernel of a call completes
+ * only after the kernels of all earlier calls on the workspace, so a kernel
+ * enqueued behind a call without this flag sees the call's result. */
 #define VKOP_FLAG_INPUT_READY 1
 
 /* Library version (VKOP_CUDA_VERSION of the build). */
