@@ -377,16 +377,16 @@ def run_vocab_sharded(args, rank, local_rank, world):
             "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
             "config": {"workload": args.workload, "rows": rows, "cols": cols, "cols_per_gpu": hi - lo, "k": k,
                        "sharding": f"vocab x{world}", "exchange": ("NCCL all-gather of per-row packets" if args.exchange == "nccl" or world == 1
-                                    else "stores into peer memory + flags (NVLink)") + " + merge kernel",
+                                    else "stores into peer memory + flags (NVLink)" + (", C++ operator" if args.exchange == "native" else "")) + " + merge kernel",
                        "launch": "host",
                        "packet_bytes_per_rank": rows * (4 + 2 * k) * 4,
                        "l2": f"inputs rotate over {NBUF} buffers ({NBUF * rows * (hi - lo) * esz >> 20} MiB per rank)"},
             "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
                          "frac": nbytes / (ms * 1e-3) / 1e9 / (peak * world), "traffic": None, "peak_kind": peak_kind}}))
     if world > 1:
-        if op.peer is not None:
+        if op.peer is not None or op.native is not None:
             dist.barrier()
-            op.peer.close()
+            op.close()
         dist.destroy_process_group()
 
 
@@ -405,13 +405,14 @@ def measure_vocab_sharded(args, rank, world, dev, dist, barrier, max_over_ranks)
     slices = [workloads.spiked_normal(rows, hi - lo, max(1, 32 // world), 9.0, 1.5, 7000 + 100 * rank + b, dtype).to(dev)
               for b in range(nbuf)]
     exchange = "none" if world == 1 else args.exchange
+    # one GPU: the C++ operator too (partial + merge, no exchange)
+    want = "native" if (world == 1 and args.exchange == "native") else ("nccl" if world == 1 else args.exchange)
     try:
-        op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev,
-                                             exchange="peer" if exchange == "peer" else "nccl")
+        op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev, exchange=want)
     except Exception as e:  # peer mapping refused (no peer access between these GPUs): the all-gather still works
-        if exchange != "peer":
+        if want == "nccl" or world == 1:
             raise
-        exchange = f"nccl (peer exchange unavailable: {type(e).__name__})"
+        exchange = f"nccl ({want} exchange unavailable: {type(e).__name__})"
         op = sharded.VocabShardedSoftmaxTopk(rows, hi - lo, lo, k, dtype, inv_t, device=dev, exchange="nccl")
     steps = max(5, min(args.steps, 100))
     for i in range(max(args.warmup, 3)):
@@ -425,15 +426,19 @@ def measure_vocab_sharded(args, rank, world, dev, dist, barrier, max_over_ranks)
     e1.record()
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1) / steps)
-    if op.peer is not None:
+    timed_out = op.timed_out()
+    if op.peer is not None or op.native is not None:
         barrier()
-        op.peer.close()
+        op.close()
+    if timed_out:
+        raise SystemExit("bench.py: a bounded wait for the peers' packets gave up")
     esz = slices[0].element_size()
     nbytes = rows * cols * esz + rows * k * (esz + 4)
     peak, peak_kind = measured_peak()
     return {"workload": name, "rows": rows, "cols": cols, "cols_per_gpu": hi - lo, "k": k, "n_gpus": world,
             "ms_per_step": ms, "steps": steps, "value": rows / (ms * 1e-3), "unit": "rows/s", "scaling": "strong",
             "exchange": {"none": "none (one GPU holds every column)", "peer": "stores into peer memory + flags (NVLink), then the merge kernel",
+                         "native": "stores into peer memory + flags (NVLink), then the merge kernel; the step is one call of the C++ operator ops::SoftmaxTopkSharded",
                          "nccl": "NCCL all-gather of per-row packets, then the merge kernel"}.get(exchange, exchange),
             "launch": "host", "packet_bytes_per_rank": rows * (4 + 2 * k) * 4,
             "hbm_frac_of_n_gpus": nbytes / (ms * 1e-3) / 1e9 / (peak * world), "peak_kind": peak_kind,
@@ -461,8 +466,10 @@ def main():
     ap.add_argument("--sharding", default="rows", choices=["rows", "vocab"],
                     help="N > 1: rows = every rank its own batch (weak scaling, no collective); vocab = the columns of "
                          "one batch split over the ranks, packets all-gathered and merged (strong scaling)")
-    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
-                    help="vocabulary sharding: how the packets travel (stores into peer memory, or an NCCL all-gather)")
+    ap.add_argument("--exchange", default="native", choices=["nccl", "peer", "native"],
+                    help="vocabulary sharding: how the packets travel (native: stores into peer memory, the whole step owned by "
+                         "the C++ operator ops::SoftmaxTopkSharded; peer: the same exchange orchestrated from Python; nccl: an "
+                         "NCCL all-gather)")
     ap.add_argument("--graph-steps", type=int, default=256, help="steps captured in the CUDA graph that is replayed")
     args = ap.parse_args()
 

@@ -176,6 +176,16 @@ def test_c_abi_library_exports_every_declared_symbol():
     assert lib.vkop_cuda_packet_bytes(64) == (4 + 128) * 4
 
 
+def test_host_library_exports_its_entry_points():
+    """libvkop_host.so (the C++ operator API and its flat C entry points) loads without a device and exports
+    what the Python front end binds, the vocabulary-sharded operator included."""
+    from vkop_b200 import host_api
+    lib = ctypes.CDLL(host_api.HOST_LIB_PATH)
+    for name in host_api.EXPORTS:
+        assert hasattr(lib, name), name
+    assert any(n.startswith("vkop_host_sharded_") for n in host_api.EXPORTS)
+
+
 def test_workspace_planning_needs_no_device():
     from vkop_b200 import capi
     d = capi.SoftmaxTopkDesc(rows=64, cols=128256, row_stride=128256, dtype=capi.F32, k=50, index_dtype=capi.I32,

@@ -57,19 +57,18 @@ def _worker(rank: int, world: int, port: int, q, exchange: str = "nccl"):
             assert torch.equal(i, i2) and torch.equal(v, v2)
             util.assert_indices_equal(iy, wiy, f"rank {rank}, second input")
             util.assert_probs_close(vy, wvy, x.dtype, f"rank {rank}, second input")
-            if op.peer is not None:
-                assert not op.peer.timed_out()
+            assert not op.timed_out()
         except AssertionError as e:
             ok = str(e)
         q.put((rank, ok))
-        if op.peer is not None:
+        if op.peer is not None or op.native is not None:
             dist.barrier()  # no rank unmaps while another may still store into its memory
-            op.peer.close()
+            op.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer", "native"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_vocab_sharded(world, exchange):
     if torch.cuda.device_count() < world:
@@ -178,3 +177,54 @@ def test_all_ranks_exchange_in_one_launch():
             util.assert_indices_equal(i, wi, f"rank {r}, step {seq}")
             util.assert_probs_close(v, wv, x.dtype, f"rank {r}, step {seq}")
         assert status.cpu().tolist() == [0] * world, "a bounded wait ran out"
+
+
+def test_native_sharded_operator_on_one_gpu():
+    """ops::SoftmaxTopkSharded through its flat C entry points.  One rank: partial + merge.  Two ranks living in one
+    process on one GPU (connect_local): both begin (partial + push), then both finish (wait + merge), all on one
+    stream, so that no kernel ever waits for one that is enqueued behind it."""
+    import oracle  # noqa: F401
+    from tests import util
+    from vkop_b200 import capi, host_api, workloads
+    from vkop_b200.sharded import split_even
+
+    rows, cols, k = 48, 131072, 64
+    x = workloads.sharded_vocab(rows=rows, cols=cols)
+    xg = x.cuda()
+    wv, wi = util.oracle_softmax_topk(x, k)
+    dt = capi._TORCH_DTYPE[x.dtype]
+    stream = torch.cuda.current_stream().cuda_stream
+    # one rank holds every column
+    one = host_api.ShardedRank(0, 0, 1, rows, cols, 0, k, dt)
+    v = torch.empty((rows, k), dtype=x.dtype, device="cuda")
+    i = torch.empty((rows, k), dtype=torch.int32, device="cuda")
+    one.run(xg.data_ptr(), v.data_ptr(), i.data_ptr(), stream)
+    torch.cuda.synchronize()
+    util.assert_indices_equal(i, wi, "one rank")
+    util.assert_probs_close(v, wv, x.dtype, "one rank")
+    one.close()
+    # three ranks of this process
+    world = 3
+    shards, ranks, outs = [], [], []
+    for r in range(world):
+        lo, hi = split_even(cols, world, r)
+        shards.append(xg[:, lo:hi].contiguous())
+        ranks.append(host_api.ShardedRank(0, r, world, rows, hi - lo, lo, k, dt, capi.I64))
+        outs.append((torch.zeros((rows, k), dtype=x.dtype, device="cuda"), torch.zeros((rows, k), dtype=torch.int64, device="cuda")))
+    for r in ranks:
+        r.connect_local(ranks)
+    y = workloads.sharded_vocab(rows=rows, cols=cols, seed=5)
+    yshards = [y.cuda()[:, split_even(cols, world, r)[0]:split_even(cols, world, r)[1]].contiguous() for r in range(world)]
+    for step in range(7):  # the receive slots are two steps deep: many steps, alternating inputs
+        src = shards if step % 2 == 0 else yshards
+        for r in range(world):
+            ranks[r].begin(src[r].data_ptr(), stream)
+        for r in range(world):
+            ranks[r].finish(outs[r][0].data_ptr(), outs[r][1].data_ptr(), stream)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert not ranks[r].timed_out()
+        util.assert_indices_equal(outs[r][1], wi, f"rank {r} of {world}")
+        util.assert_probs_close(outs[r][0], wv, x.dtype, f"rank {r} of {world}")
+    for r in ranks:
+        r.close()

@@ -98,7 +98,8 @@ def _stale(target: str, sources) -> bool:
 def build_host(force: bool = False) -> str:
     """The C++ operator API (host side) above the C ABI: libvkop_host.so, built with g++."""
     build(force=False)
-    srcs = [os.path.join(HOST, "src", "runtime.cpp"), os.path.join(HOST, "src", "host_capi.cpp")]
+    srcs = [os.path.join(HOST, "src", "runtime.cpp"), os.path.join(HOST, "src", "host_capi.cpp"),
+            os.path.join(HOST, "src", "sharded_capi.cpp")]
     deps = srcs + [os.path.join(HOST, "include"), os.path.join(ROOT, "include"), LIB]
     if force or _stale(HOST_LIB, deps):
         cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-I", os.path.join(HOST, "include"),

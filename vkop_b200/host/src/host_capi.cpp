@@ -65,6 +65,8 @@ void run(Pipeline &p, const void *host_logits, void *host_values, int32_t *host_
 extern "C" {
 
 const char *vkop_host_last_error(void) { return g_error.c_str(); }
+// (for the other translation units of this library)
+void vkop_host_set_error(const char *text) { g_error = text ? text : ""; }
 
 // dtype: vkop_dtype.  fuse != 0: the registered Softmax + TopK pair runs as the fused operator.
 void *vkop_host_pipeline_create(int device, int rows, int cols, int dtype, int k, float temperature, int fuse) {

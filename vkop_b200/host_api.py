@@ -16,7 +16,10 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB_PATH = os.path.join(HERE, "libvkop_host.so")
 EXPORTS = ("vkop_host_pipeline_create", "vkop_host_pipeline_run", "vkop_host_pipeline_destroy", "vkop_host_last_error",
-           "vkop_host_model_describe", "vkop_host_model_run")
+           "vkop_host_model_describe", "vkop_host_model_run",
+           "vkop_host_sharded_create", "vkop_host_sharded_destroy", "vkop_host_sharded_ipc_handle", "vkop_host_sharded_connect",
+           "vkop_host_sharded_connect_local", "vkop_host_sharded_begin", "vkop_host_sharded_finish", "vkop_host_sharded_run",
+           "vkop_host_sharded_timed_out")
 
 _lib = None
 
@@ -33,6 +36,17 @@ def lib() -> C.CDLL:
         L.vkop_host_pipeline_run.argtypes = [C.c_void_p] * 5
         L.vkop_host_pipeline_destroy.argtypes = [C.c_void_p]
         L.vkop_host_last_error.restype = C.c_char_p
+        L.vkop_host_sharded_create.restype = C.c_void_p
+        L.vkop_host_sharded_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                               C.c_float, C.c_uint]
+        L.vkop_host_sharded_destroy.argtypes = [C.c_void_p]
+        L.vkop_host_sharded_ipc_handle.argtypes = [C.c_void_p, C.c_void_p]
+        L.vkop_host_sharded_connect.argtypes = [C.c_void_p, C.c_void_p]
+        L.vkop_host_sharded_connect_local.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        L.vkop_host_sharded_begin.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.vkop_host_sharded_finish.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.vkop_host_sharded_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.vkop_host_sharded_timed_out.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
         _lib = L
     return _lib
 
@@ -68,6 +82,65 @@ class HostPipeline:
     def close(self):
         if self._h:
             lib().vkop_host_pipeline_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ShardedRank:
+    """One rank of the vocabulary-sharded fused Softmax + TopK, owned by the C++ operator ops::SoftmaxTopkSharded
+    (scratch, receive buffer, IPC mapping, step numbers, the partial -> push -> wait -> merge chain).  The caller
+    moves the 64-byte handles between the ranks: `handle()` on every rank, `connect(all handles in rank order)`,
+    a barrier, then `run` (or `begin` on every rank followed by `finish`).  Ranks of one process use
+    `connect_local(list of ShardedRank)`.  Pointers are raw device addresses; `stream` is a cudaStream_t."""
+
+    def __init__(self, device: int, rank: int, world: int, rows: int, cols_local: int, col_offset: int, k: int, dtype: int,
+                 index_dtype: int = 0, inv_temperature: float = 1.0, max_polls: int = 0):
+        self.rank, self.world = rank, world
+        self._h = lib().vkop_host_sharded_create(device, rank, world, rows, cols_local, col_offset, k, dtype, index_dtype,
+                                                 float(inv_temperature), max_polls)
+        if not self._h:
+            raise RuntimeError("vkop_host_sharded_create: " + lib().vkop_host_last_error().decode())
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise RuntimeError(f"{what}: status {rc}: " + lib().vkop_host_last_error().decode())
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        self._check(lib().vkop_host_sharded_ipc_handle(self._h, buf), "vkop_host_sharded_ipc_handle")
+        return buf.raw
+
+    def connect(self, handles) -> None:
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.world
+        self._check(lib().vkop_host_sharded_connect(self._h, blob), "vkop_host_sharded_connect")
+
+    def connect_local(self, ranks) -> None:
+        arr = (C.c_void_p * self.world)(*[r._h for r in ranks])
+        self._check(lib().vkop_host_sharded_connect_local(self._h, arr), "vkop_host_sharded_connect_local")
+
+    def begin(self, logits_ptr: int, stream: int = 0) -> None:
+        self._check(lib().vkop_host_sharded_begin(self._h, logits_ptr, stream), "vkop_host_sharded_begin")
+
+    def finish(self, values_ptr: int, indices_ptr: int, stream: int = 0) -> None:
+        self._check(lib().vkop_host_sharded_finish(self._h, values_ptr, indices_ptr, stream), "vkop_host_sharded_finish")
+
+    def run(self, logits_ptr: int, values_ptr: int, indices_ptr: int, stream: int = 0) -> None:
+        self._check(lib().vkop_host_sharded_run(self._h, logits_ptr, values_ptr, indices_ptr, stream), "vkop_host_sharded_run")
+
+    def timed_out(self) -> bool:
+        t = C.c_int(0)
+        self._check(lib().vkop_host_sharded_timed_out(self._h, C.byref(t)), "vkop_host_sharded_timed_out")
+        return bool(t.value)
+
+    def close(self) -> None:
+        if self._h:
+            lib().vkop_host_sharded_destroy(self._h)
             self._h = None
 
     def __del__(self):

@@ -147,7 +147,9 @@ class VocabShardedSoftmaxTopk:
     def __init__(self, rows: int, shard_cols: int, index_offset: int, k: int, dtype: torch.dtype,
                  inv_temperature: float = 1.0, index_dtype: int = 0, group=None, device=None, exchange: str = "nccl"):
         """exchange: "nccl" = all-gather of the packets through the process group; "peer" = stores into peer
-        memory (PeerPacketExchange; CUDA devices of one node)."""
+        memory, orchestrated here (PeerPacketExchange; CUDA devices of one node); "native" = the same exchange
+        owned by the C++ operator ops::SoftmaxTopkSharded (one call per step; this class only carries the IPC
+        handles through the process group)."""
         from . import capi
 
         self.capi = capi
@@ -166,9 +168,40 @@ class VocabShardedSoftmaxTopk:
                                     index_offset=index_offset)
         self.workspace = capi.Workspace(capi.softmax_topk_workspace_bytes(desc), dev)
         self.peer = PeerPacketExchange(rows, words, group, dev) if (exchange == "peer" and self.world > 1) else None
+        self.native = None
+        if exchange == "native":
+            from . import host_api
+
+            rank = dist.get_rank(group) if self.world > 1 else 0
+            self.native = host_api.ShardedRank(dev.index if dev.index is not None else torch.cuda.current_device(), rank,
+                                               self.world, rows, shard_cols, index_offset, k, capi._TORCH_DTYPE[dtype],
+                                               index_dtype, inv_temperature)
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, self.native.handle(), group=group)
+                self.native.connect(handles)
+                dist.barrier(group=group)  # nobody pushes before every rank has mapped its peers
+
+    def timed_out(self) -> bool:
+        """After a synchronisation: has a bounded wait for the peers' packets ever given up?"""
+        if self.native is not None:
+            return self.native.timed_out()
+        return self.peer.timed_out() if self.peer is not None else False
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers (call it on every rank, after a barrier)."""
+        if self.native is not None:
+            self.native.close()
+            self.native = None
+        if self.peer is not None:
+            self.peer.close()
 
     def __call__(self, shard_logits: torch.Tensor):
         capi = self.capi
+        if self.native is not None:
+            self.native.run(shard_logits.data_ptr(), self.values.data_ptr(), self.indices.data_ptr(),
+                            torch.cuda.current_stream(shard_logits.device).cuda_stream)
+            return self.values, self.indices
         capi.softmax_topk_partial(shard_logits, self.k, self.index_offset, self.inv_t, workspace=self.workspace,
                                   packets=self.packets)
         if self.peer is not None:
