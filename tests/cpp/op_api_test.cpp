@@ -8,9 +8,11 @@
 #include <cstdio>
 #include <cstdlib>
 #include <functional>
+#include <memory>
 
 #include "core/runtime.hpp"
 #include "ops/OperatorFactory.hpp"
+#include "ops/SoftmaxTopkSharded.hpp"
 
 extern "C" {
 int oracle_softmax_topk(const void *logits, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int k,
@@ -305,6 +307,76 @@ static void test_errors(Env &env) {
     EXPECT(threw, "k > axis length must be rejected");
 }
 
+// The vocabulary-sharded operator, two ranks of this process on one device: each holds half the columns
+// of the same logits; both must end with the k best of the whole row (softmax over all columns).
+static void test_sharded(Env &) {
+    const int rows = 16, cols = 40000, k = 10, world = 2;
+    Lcg rng(77);
+    std::vector<float> x(static_cast<size_t>(rows) * cols);
+    for (auto &v : x)
+        v = rng.normal() * 2.0f;
+    std::vector<float> wv(static_cast<size_t>(rows) * k);
+    std::vector<int64_t> wi(wv.size());
+    oracle_softmax_topk(x.data(), 0, rows, cols, cols, k, 1.0f, 0, 0, 0, wv.data(), wi.data());
+    const int half = cols / world;
+    std::vector<std::unique_ptr<ops::SoftmaxTopkSharded>> ranks;
+    std::vector<float *> d_logits(world), d_values(world);
+    std::vector<int *> d_indices(world);
+    for (int r = 0; r < world; r++) {
+        ops::SoftmaxTopkSharded::Config c;
+        c.rank = r;
+        c.world = world;
+        c.rows = rows;
+        c.cols_local = half;
+        c.col_offset = static_cast<int64_t>(r) * half;
+        c.k = k;
+        ranks.emplace_back(new ops::SoftmaxTopkSharded(c));
+        cudaMalloc(&d_logits[r], sizeof(float) * rows * half);
+        cudaMalloc(&d_values[r], sizeof(float) * rows * k);
+        cudaMalloc(&d_indices[r], sizeof(int) * rows * k);
+        cudaMemcpy2D(d_logits[r], sizeof(float) * half, x.data() + static_cast<size_t>(r) * half, sizeof(float) * cols,
+                     sizeof(float) * half, rows, cudaMemcpyHostToDevice);
+    }
+    std::vector<ops::SoftmaxTopkSharded *> peers;
+    for (auto &r : ranks)
+        peers.push_back(r.get());
+    for (auto &r : ranks)
+        r->connect_local(peers.data());
+    for (int step = 0; step < 3; step++) {
+        for (int r = 0; r < world; r++)
+            ranks[r]->begin(d_logits[r], nullptr);
+        for (int r = 0; r < world; r++)
+            ranks[r]->finish(d_values[r], d_indices[r], nullptr);
+    }
+    cudaDeviceSynchronize();
+    for (int r = 0; r < world; r++) {
+        EXPECT(!ranks[r]->timed_out(), "sharded rank %d: a wait gave up", r);
+        std::vector<float> v(wv.size());
+        std::vector<int> idx(wv.size());
+        cudaMemcpy(v.data(), d_values[r], sizeof(float) * v.size(), cudaMemcpyDeviceToHost);
+        cudaMemcpy(idx.data(), d_indices[r], sizeof(int) * idx.size(), cudaMemcpyDeviceToHost);
+        for (size_t i = 0; i < v.size(); i++) {
+            EXPECT(idx[i] == static_cast<int>(wi[i]), "sharded rank %d index %zu: %d vs %lld", r, i, idx[i], static_cast<long long>(wi[i]));
+            EXPECT(std::fabs(v[i] - wv[i]) <= 1e-6f + 1e-5f * std::fabs(wv[i]), "sharded rank %d value %zu: %g vs %g", r, i, v[i], wv[i]);
+        }
+        cudaFree(d_logits[r]);
+        cudaFree(d_values[r]);
+        cudaFree(d_indices[r]);
+    }
+    bool threw = false;
+    try {
+        ops::SoftmaxTopkSharded::Config c;
+        c.world = 2;
+        c.rank = 2;
+        c.rows = 1;
+        c.cols_local = 10;
+        ops::SoftmaxTopkSharded bad(c);
+    } catch (const std::invalid_argument &) {
+        threw = true;
+    }
+    EXPECT(threw, "a rank outside the world must be rejected");
+}
+
 int main() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -319,6 +391,7 @@ int main() {
     test_nms(env);
     test_runtime_pipeline(env);
     test_errors(env);
+    test_sharded(env);
     std::printf(g_failures ? "%d FAILURES\n" : "all operator API cases passed\n", g_failures);
     return g_failures ? 1 : 0;
 }
