@@ -119,6 +119,9 @@ static int run_select(const vkop_softmax_topk_desc &d, const void *in, void *ov,
 
 using namespace vkop_cuda;
 
+// see vkop_cuda_workspace_init
+static __global__ void workspace_ready_kernel() {}
+
 extern "C" {
 
 int vkop_cuda_version(void) { return VKOP_CUDA_VERSION; }
@@ -142,8 +145,16 @@ int vkop_cuda_workspace_init(void *workspace, size_t bytes, void *stream) {
         return VKOP_OK;
     if (!workspace)
         return VKOP_INVALID_ARG;
-    return cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream)) == cudaSuccess ? VKOP_OK
-                                                                                                   : VKOP_CUDA_ERROR;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(workspace, 0, bytes, s) != cudaSuccess)
+        return VKOP_CUDA_ERROR;
+    // A kernel launched with programmatic stream serialization that does not wait for its predecessor
+    // (a call with VKOP_FLAG_INPUT_READY) may start as soon as that predecessor's blocks have ended,
+    // before its writes are flushed.  With this empty kernel behind the clearing, such a call's
+    // predecessor is a kernel that wrote nothing and that itself started after the cleared bytes were
+    // visible: the call reads zeros, not what the memory held before.
+    workspace_ready_kernel<<<1, 32, 0, s>>>();
+    return cudaGetLastError() == cudaSuccess ? VKOP_OK : VKOP_CUDA_ERROR;
 }
 
 int vkop_cuda_softmax_topk_workspace(const vkop_softmax_topk_desc *desc, size_t *bytes) {

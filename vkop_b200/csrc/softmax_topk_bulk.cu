@@ -31,8 +31,14 @@
 // tightens the bound once more on the candidates themselves, ranks the survivors by counting and
 // writes the k results.  It runs beside the next call's streaming CTAs.
 //
-// With VKOP_FLAG_INPUT_READY consecutive calls overlap: the scratch pools are used in turn (kBulkSets sets), and a per-row counter of finished calls keeps the results of a row in call order
-// and tells when a set may be written again.  Calls number themselves on the device.
+// Order between calls.  Neither kernel touches global memory before it lets its successor in.  With
+// VKOP_FLAG_INPUT_READY the streaming CTAs of a call read their logits beside the previous call; what
+// they WRITE (the part's pool and header) they write after griddepcontrol.wait at the end of the
+// part, that is, after the selection of the previous call has completed.  That selection has read
+// the one set of scratch pools there is, and, since it waited for its own streaming kernel, which
+// waited for the selection before it, the completed kernels form an unbroken chain: selections run
+// one after the other and results reach the outputs in call order.  No call numbers, no counters.
+// Without the flag the streaming kernel waits before its first read instead.
 //
 // Every wait in these kernels is bounded (about a second): a wait that runs out sets an abort flag
 // and VKOP_TIMEOUT in the workspace status word; the CTA stops issuing copies, walks on without
@@ -57,14 +63,13 @@ namespace vkop_cuda {
 #endif
 constexpr int kBulkConsumers = 256;                 // consumer threads of a streaming CTA (8 warps)
 constexpr int kBulkWarps = kBulkConsumers / 32;
-constexpr int kBulkThreads = kBulkConsumers + 64;   // plus the producer warp and the control warp
+constexpr int kBulkThreads = kBulkConsumers + 32;   // plus the producer warp
 constexpr int kBulkTileVecs = VKOP_BULK_TILE_VECS;  // a tile: 16 KB, one bulk copy, consumed by all consumer warps
 constexpr int kBulkStages = VKOP_BULK_STAGES;       // tiles in the ring (48 KB)
 constexpr int kBulkJ = kBulkTileVecs / kBulkConsumers;  // vectors per consumer thread and tile
 constexpr int kBulkPool = 1024;                     // vectors the pool of a part holds
 constexpr int kBulkMaxParts = 8;                    // most parts a row is cut into
 constexpr int kBulkMinPartVecs = 2048;              // a part is at least 32 KB
-constexpr int kBulkSets = 4;                        // sets of scratch pools that consecutive calls use in turn
 constexpr int kSelThreads = 256;                    // threads of a selecting CTA
 constexpr int kSelCap = 1024;                       // candidates a row may gather before the exact fallback takes over
 constexpr int kBar = 1;                             // named barrier of the consumer threads
@@ -138,8 +143,7 @@ struct PartHeader {
     float sum;       // exp-sum of the part relative to mz
     uint32_t tkey;   // bound: at least k elements of the part reach it (0: none)
     int32_t count;   // pooled vectors, or -1: the pool is no use (NaN, or more vectors than it holds)
-    uint32_t epoch;  // number of the call on its workspace
-    uint32_t pad[3];
+    uint32_t pad[4];
 };
 constexpr size_t kPartStride = sizeof(PartHeader) + static_cast<size_t>(kBulkPool) * 20;
 static_assert(sizeof(PartHeader) == 32 && kPartStride % 16 == 0, "pooled vectors are stored as 16-byte words");
@@ -147,8 +151,7 @@ static_assert(sizeof(PartHeader) == 32 && kPartStride % 16 == 0, "pooled vectors
 struct BulkParams {
     ChunkParams c;            // logits, shape, outputs; nvv, vstride, per_cta; parts_per_row = P
     int *status;              // workspace: VKOP_OK or VKOP_TIMEOUT
-    unsigned int *epoch2, *arrive2;  // workspace: call counter and arrival counter of the selecting kernel
-    unsigned char *scratch;   // [kBulkSets][rows * P] parts of kPartStride bytes
+    unsigned char *scratch;   // [rows * P] parts of kPartStride bytes
 };
 
 // Control block of a streaming CTA, behind the arrays in dynamic shared memory.
@@ -160,10 +163,8 @@ struct BulkCtl {
     int nrec;                 // vectors in the pool (may count past its capacity)
     int nan_seen;
     uint32_t tkey;            // bound of the part as a key (0: none)
-    uint32_t epoch;           // number of this call on its workspace
-    int epoch_ready;          // the control warp has drawn it
     int abort;
-    int pad[2];
+    int pad[4];
 };
 
 // Dynamic shared memory of the streaming kernel: tile rings | pool of recorded vectors | their places | control.
@@ -240,7 +241,6 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
         ctl->nan_seen = 0;
         ctl->tkey = 0;
         ctl->abort = 0;
-        ctl->epoch_ready = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     bool waited = false;
@@ -250,9 +250,8 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
     }
     __syncthreads();
     // The next kernel of the stream is let in when EVERY thread of every CTA has said so (or has
-    // exited): all threads say so now, except the one that numbers the call, which does it after that.
-    if (!(warp == NW + 1 && lane == 0))
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // exited): all threads say so at once.  Nothing in global memory is touched before this.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == NW) {
         // ================= producer warp =================
@@ -281,30 +280,6 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
         }
         return;
     }
-    if (warp == NW + 1) {
-        // ================= control warp =================
-        // One thread finds the place of this call among the calls on its workspace (needed at the end
-        // of the part): it reads the call counter and then draws an arrival ticket; the CTA that draws
-        // the last ticket of the call advances the counter.  Only then does the CTA let the next
-        // kernel of the stream in, so all CTAs of a call read the same number.
-        if (lane == 0) {
-            unsigned int e, tk;
-            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(p.epoch_word) : "memory");
-            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(tk) : "l"(p.arrive_word) : "memory");
-            if (tk == grid - 1u) {
-                *p.arrive_word = 0u;
-                const unsigned int nx = e + 1u;
-                asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(nx) : "memory");
-                __threadfence();  // performed, not just ordered, before this thread lets the next call in
-            }
-            ctl->epoch = e;
-            __threadfence_block();
-            *const_cast<volatile int *>(&ctl->epoch_ready) = 1;
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        }
-        return;
-    }
-
     // ================= consumer warps =================
     const float c1 = p.inv_t * kLog2e;
     const int cols = static_cast<int>(p.cols);
@@ -464,22 +439,14 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
         if (nan_seen)
             ctl->nan_seen = 1;
     }
-    if (tid == 0) {
-        // the call number was drawn by the control warp microseconds ago; bounded all the same
-        const volatile int *ready = &ctl->epoch_ready;
-        for (int i = 0; i < (1 << 22) && !*ready; i++)
-            __nanosleep(32);
-        if (!*ready)
-            ctl->abort = 1;
-        // This set of pools last served the call kBulkSets calls ago: has the selection of that call
-        // read this row's pools?  (It has, unless the selections are many calls behind.)
-        const uint32_t e = ctl->epoch;
-        if (!waited && !ctl->abort && !wait_row_counter(p.row_done + row, e + 1u - kBulkSets, false))
-            ctl->abort = 1;
-    }
-    cta_sync<kBar, NC>();  // maxima, pool, bound and call number are final; the scratch set is free
-    const uint32_t epoch = ctl->epoch;
-    unsigned char *const part = bp.scratch + (static_cast<size_t>(epoch % kBulkSets) * grid + blockIdx.x) * kPartStride;
+    // Everything this CTA writes to global memory comes after the kernel before it in the stream
+    // (the selection of the previous call) has completed: that kernel has read the scratch pools this
+    // CTA is about to overwrite, and, having itself waited for its predecessor, it stands for every
+    // earlier kernel of the stream too.  The streaming above needed no such order.
+    if (!waited)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    cta_sync<kBar, NC>();  // maxima, pool and bound are final
+    unsigned char *const part = bp.scratch + static_cast<size_t>(blockIdx.x) * kPartStride;
     uint32_t mkey = 0;
 #pragma unroll
     for (int q = 0; q < NW; q++)
@@ -517,8 +484,7 @@ __global__ void __launch_bounds__(kBulkThreads, VKOP_BULK_CTAS_PER_SM) bulk_stre
         h.sum = S;
         h.tkey = ctl->tkey;
         h.count = (pool_bad || (need_sum && S != S)) ? -1 : n_rec;
-        h.epoch = epoch;
-        h.pad[0] = h.pad[1] = h.pad[2] = 0u;
+        h.pad[0] = h.pad[1] = h.pad[2] = h.pad[3] = 0u;
         *reinterpret_cast<uint4 *>(part) = *reinterpret_cast<const uint4 *>(&h);
         *reinterpret_cast<uint4 *>(part + 16) = *(reinterpret_cast<const uint4 *>(&h) + 1);
         if (ctl->abort && bp.status)
@@ -577,42 +543,24 @@ __global__ void __launch_bounds__(kSelThreads) bulk_select_kernel(const __grid_c
     __shared__ PartHeader s_hdr[kBulkMaxParts];
     __shared__ uint32_t s_wr[NW];
     __shared__ int s_hist[256], s_pick[4], s_count, s_n[2];
-    __shared__ uint32_t s_epoch;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = blockIdx.x;
     const int P = p.parts_per_row;
     const int cols = static_cast<int>(p.cols);
     const uint32_t nvv = static_cast<uint32_t>(p.nvv);
-    const uint32_t nparts = static_cast<uint32_t>(p.rows) * static_cast<uint32_t>(P);
-    // (the next kernel of the stream is let in when every thread of every CTA has said so: all do at
-    // once, except the one that numbers the call, which does it after that)
-    if (tid != 0)
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // the next call's streaming kernel may start at once: this kernel is small and runs beside it
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         s_n[0] = 0;
         s_n[1] = 0;
-        // The place of this call among the calls on its workspace, found as the streaming kernel finds
-        // its own (the two counts run in step): call counter, then an arrival ticket; the last CTA of
-        // the call to arrive advances the counter.  Only then is the next kernel of the stream let in.
-        unsigned int e, tk;
-        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(e) : "l"(bp.epoch2) : "memory");
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(tk) : "l"(bp.arrive2) : "memory");
-        if (tk == gridDim.x - 1u) {
-            *bp.arrive2 = 0u;
-            const unsigned int nx = e + 1u;
-            asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(bp.epoch2), "r"(nx) : "memory");
-            __threadfence();  // performed, not just ordered, before this thread lets the next call in
-        }
-        s_epoch = e;
-        // the next call's streaming kernel may start: this kernel is small and runs beside it
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
-    // everything the streaming kernel of this call wrote is visible after this
+    // Everything the streaming kernel of this call wrote is visible after this; and since that kernel
+    // waited for the selection of the previous call before it wrote, the selections of consecutive
+    // calls run one after the other: results reach the outputs in call order.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
-    const uint32_t epoch = s_epoch;
-    const unsigned char *const set = bp.scratch + static_cast<size_t>(epoch % kBulkSets) * nparts * kPartStride;
+    const unsigned char *const set = bp.scratch;
     if (tid < P)
         s_hdr[tid] = *reinterpret_cast<const PartHeader *>(set + (static_cast<size_t>(row) * P + tid) * kPartStride);
     __syncthreads();
@@ -743,16 +691,7 @@ __global__ void __launch_bounds__(kSelThreads) bulk_select_kernel(const __grid_c
         pk[2] = static_cast<uint32_t>(n < p.k ? n : p.k);
         pk[3] = 0;
     }
-    // results of one row are written in call order (the previous call's selection is rarely behind)
-    if (tid == 0 && !wait_row_counter(p.row_done + row, epoch, true) && bp.status)
-        *bp.status = VKOP_TIMEOUT;
-    __syncthreads();
     rank_emit<T>(p, row, best, n, M, S);
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int d = epoch + 1u;
-        asm volatile("st.release.gpu.u32 [%0], %1;" ::"l"(p.row_done + row), "r"(d) : "memory");
-    }
 }
 
 // ---------------------------------------------------------------------------
@@ -795,7 +734,7 @@ int plan_bulk(const vkop_softmax_topk_desc &d, bool base_aligned, BulkPlan *plan
     plan->smem_bytes = kBulkSmemBytes;
     plan->parts = P;
     plan->grid = static_cast<int>(d.rows * P);
-    plan->scratch_bytes = kBulkSets * static_cast<size_t>(d.rows) * P * kPartStride;
+    plan->scratch_bytes = static_cast<size_t>(d.rows) * P * kPartStride;
     return VKOP_OK;
 }
 
@@ -854,12 +793,7 @@ int launch_bulk(const vkop_softmax_topk_desc &d, const BulkPlan &plan, const voi
     p.parts_per_row = plan.parts;
     p.input_ready = (d.flags & VKOP_FLAG_INPUT_READY) ? 1 : 0;
     char *cw = static_cast<char *>(common_ws);
-    p.arrive_word = reinterpret_cast<unsigned int *>(cw);
-    p.epoch_word = reinterpret_cast<unsigned int *>(cw + 4);
     bp.status = reinterpret_cast<int *>(cw + 8);
-    bp.arrive2 = reinterpret_cast<unsigned int *>(cw + 12);
-    bp.epoch2 = reinterpret_cast<unsigned int *>(cw + 16);
-    p.row_done = reinterpret_cast<unsigned int *>(cw + 256);
     bp.scratch = static_cast<unsigned char *>(bulk_ws);
     switch (d.dtype) {
     case VKOP_F32: return launch_bulk_t<float>(bp, plan, stream);

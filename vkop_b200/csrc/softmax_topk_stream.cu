@@ -631,7 +631,8 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
     int parity = 0;
     // groups for the upper end of the histogram range: the smallest of their maxima should rank
     // well inside the best k thread maxima
-    const int hgroups = p.k < 4 ? 1 : p.k < 10 ? 2 : p.k < 24 ? 4 : p.k < 56 ? 8 : 16;
+    const int hgroups_k = p.k < 4 ? 1 : p.k < 10 ? 2 : p.k < 24 ? 4 : p.k < 56 ? 8 : 16;
+    const int hgroups = hgroups_k < NW ? hgroups_k : NW;  // (a group is at least one warp)
     if (tid < 256)
         s_thist[0][tid] = 0;
     uint64_t *slot = s_cand + tid;  // this thread's next private slot; past slot_end the slots are full
@@ -887,6 +888,20 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
             grid = d.rows * s;
         }
     }
+    // Several hundred rows (at least half of what the GPU holds as light CTAs, at most all of it): one
+    // 256-thread CTA per row, four to an SM, in a single wave.  One call fills the GPU by itself, no row has
+    // parts to merge, and no CTA crosses a row.
+    bool many_whole_rows = false;
+    {
+        const int64_t light_slots = 4 * static_cast<int64_t>(kNumSms);
+        const int64_t nvv_a = (d.cols + epv - 1) / epv;
+        if (d.splits == 0 && parts_per_row == 0 && d.rows >= light_slots / 2 && d.rows <= light_slots &&
+            nvv_a >= 16 * static_cast<int64_t>(kStreamThreadsSmall) * kStreamVecs) {
+            many_whole_rows = true;
+            parts_per_row = 1;
+            grid = d.rows;
+        }
+    }
     const int64_t per = (total + grid - 1) / grid;
     // parts a row can be cut into: its share of the CTAs, plus one at either end
     const int64_t maxparts = parts_per_row > 0 ? parts_per_row : (nvv + per - 1) / per + 2;
@@ -895,7 +910,7 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     // per SM, and with few parts per row the CTAs of a row form a cluster and hand their parts over
     // in shared memory.
     int threads = kStreamThreads;
-    if (overlapping && parts_per_row > 0 && maxparts <= 64 && maxparts * d.k <= 8 * kStreamThreadsSmall)
+    if ((overlapping || many_whole_rows) && parts_per_row > 0 && maxparts <= 64 && maxparts * d.k <= 8 * kStreamThreadsSmall)
         threads = kStreamThreadsSmall;
     // The CTA that merges a row gathers every part's list into one tile stage of its shared memory
     // (8 * threads slots) and selects in the two candidate regions (as many again).
@@ -914,14 +929,14 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
     plan->aligned = aligned ? 1 : 0;
     plan->parts_per_row = parts_per_row;
     // few parts per row: the CTAs of a row form a cluster and hand their parts over in shared memory
-    plan->cluster = (!overlapping && parts_per_row >= 1 && parts_per_row <= kStreamMaxCluster) ? parts_per_row : 0;
+    plan->cluster = (!overlapping && !many_whole_rows && parts_per_row >= 1 && parts_per_row <= kStreamMaxCluster) ? parts_per_row : 0;
     plan->maxparts = static_cast<int>(maxparts);
     plan->list_cap = list_cap;
     // per row: an arrival counter for each of the two sets of lists (the call counter and the rows'
     // counters of finished calls sit in the head of the workspace that the streaming kernels share)
     plan->counters_bytes = ((static_cast<size_t>(d.rows) * 2 * 4 + 255) / 256) * 256;
     plan->lists_bytes = 2 * static_cast<size_t>(d.rows) * maxparts * (2 + list_cap) * 8;
-    if (overlapping && parts_per_row == 1) {
+    if ((overlapping || many_whole_rows) && parts_per_row == 1) {
         // whole rows publish no lists; the region holds the rows' mailboxes (kMailSlots entries of two
         // addresses, k values and k indices, each block rounded up to 16 bytes)
         const size_t entry = 16 + ((static_cast<size_t>(d.k) * esz + 15) & ~static_cast<size_t>(15)) +
