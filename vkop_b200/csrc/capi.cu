@@ -49,7 +49,9 @@ static int plan_select(const vkop_softmax_topk_desc &d, const void *in, SelectPl
     int rc = VKOP_UNSUPPORTED;
     const int64_t row_bytes = d.cols * (d.dtype == VKOP_F32 ? 4 : 2);
     // rows longer than one CTA's register tile, and enough of them: the streaming kernel
-    const bool prefer_stream = row_bytes > 64 * 1024 && d.rows * row_bytes >= (2ll << 20);
+    // (several hundred rows of 32 KB and more also stream: one light CTA per row fills the GPU in one wave)
+    const bool one_wave = d.rows >= 2 * 148 && d.rows <= 4 * 148 && row_bytes >= 32 * 1024;
+    const bool prefer_stream = (row_bytes > 64 * 1024 || one_wave) && d.rows * row_bytes >= (2ll << 20);
     if (d.path == VKOP_PATH_STREAM || d.path == VKOP_PATH_BULK || (d.path == VKOP_PATH_AUTO && prefer_stream && d.splits == 0)) {
         // Two implementations serve this kind: the cp.async kernel (any alignment) and the bulk-copy
         // kernels (16-byte aligned long rows).  Both number their calls in one shared head of the

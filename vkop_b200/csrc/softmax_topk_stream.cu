@@ -896,7 +896,7 @@ int plan_stream(const vkop_softmax_topk_desc &d, bool base_aligned, StreamPlan *
         const int64_t light_slots = 4 * static_cast<int64_t>(kNumSms);
         const int64_t nvv_a = (d.cols + epv - 1) / epv;
         if (d.splits == 0 && parts_per_row == 0 && d.rows >= light_slots / 2 && d.rows <= light_slots &&
-            nvv_a >= 16 * static_cast<int64_t>(kStreamThreadsSmall) * kStreamVecs) {
+            nvv_a >= 2048) {  // (rows of 32 KB and more)
             many_whole_rows = true;
             parts_per_row = 1;
             grid = d.rows;
