@@ -361,6 +361,46 @@ def test_overlapping_whole_row_calls_deliver_in_call_order(capi, dtype, index64,
             util.assert_probs_close(seen[b][0], wv, dtype, f"buffer {b}, round {rep}")
 
 
+@pytest.mark.parametrize("rows,cols,k,dtype", [(300, 9001, 5, torch.float32),      # just long enough, odd length
+                                               (512, 32000, 64, torch.bfloat16),   # one GPU's slice of the sharded shape
+                                               (592, 20000, 128, torch.float16),   # every light CTA slot taken, largest k
+                                               (296, 70001, 50, torch.float32)])
+def test_one_wave_of_whole_rows(capi, rows, cols, k, dtype):
+    """Several hundred long rows: one light CTA per row, a single wave.  With and without VKOP_FLAG_INPUT_READY,
+    from an unaligned pointer, with ties, NaN and infinities in some rows, raw values and the smallest."""
+    g = torch.Generator().manual_seed(rows + cols + k)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+    x[1, : cols // 2] = x[1, cols // 2: 2 * (cols // 2)]  # every value twice: ties across the row
+    x[2, 17] = float("nan")
+    x[3, 5] = float("inf")
+    x[4] = 1.5  # a constant row: the lowest indices win
+    x[5, : cols - 3] = float("-inf")
+    xg = x.cuda()
+    wv, wi = util.oracle_softmax_topk(x, k, 1.25)
+    for flags in (0, capi.FLAG_INPUT_READY):
+        d = capi.make_desc(xg, k, 1.25, flags=flags)
+        ws = capi.Workspace(capi.softmax_topk_workspace_bytes(d))
+        out = (torch.empty((rows, k), dtype=dtype, device="cuda"), torch.empty((rows, k), dtype=torch.int32, device="cuda"))
+        for rep in range(3):  # (calls with the flag overlap)
+            capi.softmax_topk(xg, k, 1.25, workspace=ws, out=out, flags=flags)
+        torch.cuda.synchronize()
+        util.assert_indices_equal(out[1], wi, f"flags {flags}")
+        util.assert_probs_close(out[0], wv, dtype, f"flags {flags}")
+    # unaligned rows (a view that starts one element in), int64 indices
+    xu = xg[:, 1:]
+    wvu, wiu = util.oracle_softmax_topk(x[:, 1:].contiguous(), k, 1.0)
+    v, i = capi.softmax_topk(xu, k, 1.0, index_dtype=capi.I64)
+    torch.cuda.synchronize()
+    util.assert_indices_equal(i, wiu, "unaligned")
+    util.assert_probs_close(v, wvu, dtype, "unaligned")
+    # standalone TopK, smallest
+    kk = min(k, 17)
+    v, i = capi.softmax_topk(xg, kk, standalone_topk=True, largest=False)
+    torch.cuda.synchronize()
+    wvs, wis = oracle.topk(util.to_oracle_array(x), kk, largest=False, dtype=util.ORACLE_DTYPE[dtype])
+    assert np.array_equal(i.cpu().numpy(), wis)
+
+
 def test_stream_raw_smallest_and_packets(capi):
     g = torch.Generator().manual_seed(53)
     x = torch.randn(40, 70001, generator=g)
