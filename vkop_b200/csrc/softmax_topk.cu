@@ -259,24 +259,71 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
 }
 
 // Merge of packets gathered from several GPUs: [shards][rows][packet].
+// A packet lists its shard's best candidates best first, so the last entry of a full packet is
+// reached by k candidates of that shard alone: the largest of those entries over the shards bounds
+// the row's k-th best from below, and only candidates that reach it take part in the ranking
+// (about k + a few instead of shards * k).
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS) merge_packets_kernel(const ChunkParams p, const uint32_t *packets, int shards) {
     extern __shared__ __align__(16) uint64_t s_buf[];
     __shared__ float s_red[THREADS / 32];
     __shared__ int s_tmp[2];
-    constexpr int NW = THREADS / 32;
+    __shared__ uint32_t s_bound;
+    __shared__ int s_n;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t row = blockIdx.x;
     const int k = p.k, pw = packet_words(p.k);
     const int64_t gstride = p.rows * pw;
     const uint32_t *base = packets + row * pw;
+    const int slots = shards * k;
+    // Everything a thread needs is requested before anything is used (one round trip to the L2): its
+    // first two slots with their shard's count, and, for the first warp, the headers.
+    constexpr int PRE = 2;
+    uint32_t key[PRE], idx[PRE];
+    int cnt[PRE], jj[PRE];
+#pragma unroll
+    for (int u = 0; u < PRE; u++) {
+        const int sl = u * THREADS + tid;
+        key[u] = idx[u] = 0u;
+        cnt[u] = 0;
+        jj[u] = 0;
+        if (sl < slots) {
+            const int g = sl / k;
+            jj[u] = sl - g * k;
+            const uint32_t *pk = base + g * gstride;
+            cnt[u] = static_cast<int>(__ldg(pk + 2));
+            key[u] = __ldg(pk + 4 + jj[u]);
+            idx[u] = __ldg(pk + 4 + k + jj[u]);
+        }
+    }
     if (warp == 0) {
         float m = -INFINITY;
-        for (int g = lane; g < shards; g += 32)
-            m = fmaxf(m, __uint_as_float(__ldg(base + g * gstride)));
+        uint32_t bound = 0u;
+        float mg0 = -INFINITY, sg0 = 0.0f;  // (the usual case, at most 32 shards: this lane's header stays in registers)
+        if (lane < shards) {
+            const uint32_t *pk = base + lane * gstride;
+            mg0 = __uint_as_float(__ldg(pk));
+            sg0 = __uint_as_float(__ldg(pk + 1));
+            const int c0 = static_cast<int>(__ldg(pk + 2));
+            const uint32_t last = __ldg(pk + 4 + k - 1);
+            m = mg0;
+            if (c0 >= k)
+                bound = last;
+        }
+        for (int g = lane + 32; g < shards; g += 32) {
+            const uint32_t *pk = base + g * gstride;
+            m = fmaxf(m, __uint_as_float(__ldg(pk)));
+            if (static_cast<int>(__ldg(pk + 2)) >= k) {
+                const uint32_t last = __ldg(pk + 4 + k - 1);
+                bound = last > bound ? last : bound;
+            }
+        }
         m = warp_max(m);
+        bound = __reduce_max_sync(kFullMask, bound);
         float s = 0.0f;
-        for (int g = lane; g < shards; g += 32) {
+        if (lane < shards && sg0 != 0.0f)
+            s = sg0 * expf(mg0 - m);
+        for (int g = lane + 32; g < shards; g += 32) {
             const float mg = __uint_as_float(__ldg(base + g * gstride)), sg = __uint_as_float(__ldg(base + g * gstride + 1));
             if (sg != 0.0f)
                 s += sg * expf(mg - m);
@@ -285,19 +332,41 @@ __global__ void __launch_bounds__(THREADS) merge_packets_kernel(const ChunkParam
         if (lane == 0) {
             s_red[0] = m;
             s_red[1] = s;
+            s_bound = bound;
+            s_n = 0;
         }
     }
-    const int slots = shards * k;
-    for (int sl = tid; sl < slots; sl += THREADS) {
-        const int g = sl / k, j = sl - g * k;
-        const uint32_t *pk = base + g * gstride;
-        const int cnt = static_cast<int>(__ldg(pk + 2));
-        // entries past a part's count are padding: key 0 never beats a valid candidate and is never emitted
-        s_buf[sl] = j < cnt ? make_cand(__ldg(pk + 4 + j), __ldg(pk + 4 + k + j)) : 0ull;
+    __syncthreads();
+    const uint32_t bound = s_bound;
+    auto offer = [&](uint64_t c) {
+        const bool pass = c != 0ull && cand_key(c) >= bound;
+        const unsigned b = __ballot_sync(kFullMask, pass);
+        if (b != 0u) {
+            int at = 0;
+            if (lane == 0)
+                at = atomicAdd(&s_n, __popc(b));
+            at = __shfl_sync(kFullMask, at, 0);
+            if (pass)
+                s_buf[at + __popc(b & ((1u << lane) - 1u))] = c;
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < PRE; u++)  // (entries past a part's count are padding: key 0 is no valid candidate)
+        offer(jj[u] < cnt[u] ? make_cand(key[u], idx[u]) : 0ull);
+    for (int sl0 = PRE * THREADS; sl0 < slots; sl0 += THREADS) {
+        const int sl = sl0 + tid;
+        uint64_t c = 0ull;
+        if (sl < slots) {
+            const int g = sl / k, j = sl - g * k;
+            const uint32_t *pk = base + g * gstride;
+            if (j < static_cast<int>(__ldg(pk + 2)))
+                c = make_cand(__ldg(pk + 4 + j), __ldg(pk + 4 + k + j));
+        }
+        offer(c);
     }
     __syncthreads();
-    (void)NW;
-    select_and_emit<T, THREADS>(p, row, s_buf, slots, s_buf + ((slots + 31) & ~31), s_red[0], s_red[1], nullptr, s_tmp);
+    const int n = s_n;
+    select_and_emit<T, THREADS>(p, row, s_buf, n, s_buf + ((slots + 31) & ~31), s_red[0], s_red[1], nullptr, s_tmp);
 }
 
 // ---------------------------------------------------------------------------
