@@ -69,8 +69,13 @@ typedef enum vkop_select_path {
  * output buffer, enqueue no other kernel that writes those outputs, and let
  * every output buffer written by overlapping calls belong to one workspace.
  * Results reach the outputs in call order, and the kernel of a call completes
- * only after the kernels of all earlier calls on the workspace, so a kernel
- * enqueued behind a call without this flag sees the call's result. */
+ * only after the kernel before it in the stream has, so a kernel enqueued
+ * behind a call in the usual way sees the results of that call and of all
+ * earlier ones.  (What may sit between two such calls: calls of this library,
+ * with or without the flag, on this or another workspace, and any kernel
+ * launched in the usual way.  Not a foreign kernel launched with programmatic
+ * stream serialization that neither waits for its predecessor nor ends after
+ * it: the chain of completions would break there.) */
 #define VKOP_FLAG_INPUT_READY 1
 
 /* Library version (VKOP_CUDA_VERSION of the build). */

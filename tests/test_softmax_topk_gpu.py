@@ -401,6 +401,47 @@ def test_one_wave_of_whole_rows(capi, rows, cols, k, dtype):
     assert np.array_equal(i.cpu().numpy(), wis)
 
 
+def test_overlapping_calls_on_two_workspaces_in_turn(capi):
+    """Calls with the flag on two workspaces (two shapes, two sets of outputs) enqueued in turn on one stream, with a
+    call without the flag and a small chunk-path call thrown in: every kernel ends after the one before it, so
+    the copies enqueued behind the last call see the final results of both."""
+    g = torch.Generator().manual_seed(2024)
+    xa = [torch.randn(64, 128256, generator=g) for _ in range(3)]
+    xb = [torch.randn(96, 70001, generator=g).to(torch.float16) for _ in range(2)]
+    xs = torch.randn(8, 1000, generator=g).cuda()
+    ga, gb = [x.cuda() for x in xa], [x.cuda() for x in xb]
+    F = capi.FLAG_INPUT_READY
+    wsa = capi.Workspace(capi.softmax_topk_workspace_bytes(capi.make_desc(ga[0], 50, 1.25, flags=F)))
+    wsb = capi.Workspace(capi.softmax_topk_workspace_bytes(capi.make_desc(gb[0], 20, 1.0, flags=F)))
+    oa = (torch.zeros((64, 50), device="cuda"), torch.zeros((64, 50), dtype=torch.int32, device="cuda"))
+    ob = (torch.zeros((96, 20), dtype=torch.float16, device="cuda"), torch.zeros((96, 20), dtype=torch.int32, device="cuda"))
+
+    def enqueue():
+        for i in range(60):
+            capi.softmax_topk(ga[i % 3], 50, 1.25, workspace=wsa, out=oa, flags=F)
+            capi.softmax_topk(gb[i % 2], 20, 1.0, workspace=wsb, out=ob, flags=F)
+            if i % 16 == 5:
+                capi.softmax_topk(xs, 5)  # chunk path, launched in the usual way
+
+    enqueue()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        enqueue()
+    wa = util.oracle_softmax_topk(xa[59 % 3], 50, 1.25)
+    wb = util.oracle_softmax_topk(xb[59 % 2], 20, 1.0)
+    for rep in range(3):
+        oa[1].zero_()
+        ob[1].zero_()
+        graph.replay()
+        seen = (oa[0].clone(), oa[1].clone(), ob[0].clone(), ob[1].clone())
+        torch.cuda.synchronize()
+        util.assert_indices_equal(seen[1], wa[1], f"workspace A, round {rep}")
+        util.assert_probs_close(seen[0], wa[0], torch.float32, f"workspace A, round {rep}")
+        util.assert_indices_equal(seen[3], wb[1], f"workspace B, round {rep}")
+        util.assert_probs_close(seen[2], wb[0], torch.float16, f"workspace B, round {rep}")
+
+
 def test_stream_raw_smallest_and_packets(capi):
     g = torch.Generator().manual_seed(53)
     x = torch.randn(40, 70001, generator=g)

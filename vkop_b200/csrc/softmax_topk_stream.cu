@@ -842,9 +842,10 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_stream_k
         if (!has_next)
             break;
     }
-    // Whole rows in overlapping calls: a result may have been left for a CTA of an earlier kernel to
-    // deliver, so this kernel must not complete before its predecessor has: one CTA waits for it.
-    if (!CLUSTER && parts == 1 && blockIdx.x == 0 && !waited)
+    // Overlapping calls: a kernel must not complete before its predecessor has (with whole rows a result may
+    // have been left for a CTA of an earlier kernel to deliver; in every shape, whatever is enqueued behind a
+    // call may overwrite the logits of the calls before it): one CTA waits for the previous kernel.
+    if (!CLUSTER && blockIdx.x == 0 && !waited)
         asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
