@@ -259,58 +259,34 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) softmax_topk_chunk_ke
 }
 
 // Merge of packets gathered from several GPUs: [shards][rows][packet].
-// A packet lists its shard's best candidates best first, so the last entry of a full packet is
-// reached by k candidates of that shard alone: the largest of those entries over the shards bounds
-// the row's k-th best from below, and only candidates that reach it take part in the ranking
-// (about k + a few instead of shards * k).
+// A packet lists its shard's candidates best first, so the lists are sorted: the rank of a candidate in
+// the row is its place in its own list plus, for every other list, the number of entries there that beat
+// it, found by binary search (candidates are distinct 64-bit values, key then lower index, so the order
+// is total).  One thread per candidate, no sort, no compaction, one barrier.  A full packet's last entry
+// is reached by k candidates of its shard alone, so candidates below the largest of those last entries
+// cannot be among the row's k best and are not ranked at all.
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS) merge_packets_kernel(const ChunkParams p, const uint32_t *packets, int shards) {
-    extern __shared__ __align__(16) uint64_t s_buf[];
-    __shared__ float s_red[THREADS / 32];
-    __shared__ int s_tmp[2];
+    extern __shared__ __align__(16) uint64_t s_buf[];  // [shards][k], padding entries 0 (below every candidate)
+    __shared__ float s_red[2];
     __shared__ uint32_t s_bound;
-    __shared__ int s_n;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t row = blockIdx.x;
     const int k = p.k, pw = packet_words(p.k);
     const int64_t gstride = p.rows * pw;
     const uint32_t *base = packets + row * pw;
     const int slots = shards * k;
-    // Everything a thread needs is requested before anything is used (one round trip to the L2): its
-    // first two slots with their shard's count, and, for the first warp, the headers.
-    constexpr int PRE = 2;
-    uint32_t key[PRE], idx[PRE];
-    int cnt[PRE], jj[PRE];
-#pragma unroll
-    for (int u = 0; u < PRE; u++) {
-        const int sl = u * THREADS + tid;
-        key[u] = idx[u] = 0u;
-        cnt[u] = 0;
-        jj[u] = 0;
-        if (sl < slots) {
-            const int g = sl / k;
-            jj[u] = sl - g * k;
-            const uint32_t *pk = base + g * gstride;
-            cnt[u] = static_cast<int>(__ldg(pk + 2));
-            key[u] = __ldg(pk + 4 + jj[u]);
-            idx[u] = __ldg(pk + 4 + k + jj[u]);
-        }
+    for (int sl = tid; sl < slots; sl += THREADS) {
+        const int g = sl / k, j = sl - g * k;
+        const uint32_t *pk = base + g * gstride;
+        const int cnt = static_cast<int>(__ldg(pk + 2));
+        const uint32_t key = __ldg(pk + 4 + j), idx = __ldg(pk + 4 + k + j);
+        s_buf[sl] = j < cnt ? make_cand(key, idx) : 0ull;
     }
     if (warp == 0) {
         float m = -INFINITY;
         uint32_t bound = 0u;
-        float mg0 = -INFINITY, sg0 = 0.0f;  // (the usual case, at most 32 shards: this lane's header stays in registers)
-        if (lane < shards) {
-            const uint32_t *pk = base + lane * gstride;
-            mg0 = __uint_as_float(__ldg(pk));
-            sg0 = __uint_as_float(__ldg(pk + 1));
-            const int c0 = static_cast<int>(__ldg(pk + 2));
-            const uint32_t last = __ldg(pk + 4 + k - 1);
-            m = mg0;
-            if (c0 >= k)
-                bound = last;
-        }
-        for (int g = lane + 32; g < shards; g += 32) {
+        for (int g = lane; g < shards; g += 32) {
             const uint32_t *pk = base + g * gstride;
             m = fmaxf(m, __uint_as_float(__ldg(pk)));
             if (static_cast<int>(__ldg(pk + 2)) >= k) {
@@ -321,9 +297,7 @@ __global__ void __launch_bounds__(THREADS) merge_packets_kernel(const ChunkParam
         m = warp_max(m);
         bound = __reduce_max_sync(kFullMask, bound);
         float s = 0.0f;
-        if (lane < shards && sg0 != 0.0f)
-            s = sg0 * expf(mg0 - m);
-        for (int g = lane + 32; g < shards; g += 32) {
+        for (int g = lane; g < shards; g += 32) {
             const float mg = __uint_as_float(__ldg(base + g * gstride)), sg = __uint_as_float(__ldg(base + g * gstride + 1));
             if (sg != 0.0f)
                 s += sg * expf(mg - m);
@@ -333,40 +307,34 @@ __global__ void __launch_bounds__(THREADS) merge_packets_kernel(const ChunkParam
             s_red[0] = m;
             s_red[1] = s;
             s_bound = bound;
-            s_n = 0;
         }
     }
     __syncthreads();
+    const float M = s_red[0], S = s_red[1];
     const uint32_t bound = s_bound;
-    auto offer = [&](uint64_t c) {
-        const bool pass = c != 0ull && cand_key(c) >= bound;
-        const unsigned b = __ballot_sync(kFullMask, pass);
-        if (b != 0u) {
-            int at = 0;
-            if (lane == 0)
-                at = atomicAdd(&s_n, __popc(b));
-            at = __shfl_sync(kFullMask, at, 0);
-            if (pass)
-                s_buf[at + __popc(b & ((1u << lane) - 1u))] = c;
+    for (int sl = tid; sl < slots; sl += THREADS) {
+        const uint64_t c = s_buf[sl];
+        if (c == 0ull || cand_key(c) < bound)
+            continue;
+        const int g = sl / k;
+        int rank = sl - g * k;
+        for (int g2 = 0; g2 < shards && rank < k; g2++) {
+            if (g2 == g)
+                continue;
+            const uint64_t *a = s_buf + g2 * k;  // sorted descending: how many of its entries beat c
+            int lo = 0, hi = k;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (a[mid] > c)
+                    lo = mid + 1;
+                else
+                    hi = mid;
+            }
+            rank += lo;
         }
-    };
-#pragma unroll
-    for (int u = 0; u < PRE; u++)  // (entries past a part's count are padding: key 0 is no valid candidate)
-        offer(jj[u] < cnt[u] ? make_cand(key[u], idx[u]) : 0ull);
-    for (int sl0 = PRE * THREADS; sl0 < slots; sl0 += THREADS) {
-        const int sl = sl0 + tid;
-        uint64_t c = 0ull;
-        if (sl < slots) {
-            const int g = sl / k, j = sl - g * k;
-            const uint32_t *pk = base + g * gstride;
-            if (j < static_cast<int>(__ldg(pk + 2)))
-                c = make_cand(__ldg(pk + 4 + j), __ldg(pk + 4 + k + j));
-        }
-        offer(c);
+        if (rank < k)
+            emit<T>(p, row, rank, c, M, S, nullptr);
     }
-    __syncthreads();
-    const int n = s_n;
-    select_and_emit<T, THREADS>(p, row, s_buf, n, s_buf + ((slots + 31) & ~31), s_red[0], s_red[1], nullptr, s_tmp);
 }
 
 // ---------------------------------------------------------------------------
