@@ -230,6 +230,27 @@ def test_planner_serves_every_shape_and_flag_without_a_device():
     assert served > 5000
 
 
+def test_workspace_holds_the_rows_mailboxes():
+    """Shapes that run one CTA per row keep, per row, an order word, a ticket counter and a mailbox of 16 entries
+    (two addresses, k values, k indices, each block rounded up to 16 bytes): the planned scratch size must cover
+    them, whatever the alignment of the logits turns out to be at the call."""
+    from vkop_b200 import capi
+
+    def up16(n):
+        return (n + 15) // 16 * 16
+
+    for rows, cols, flags in ((64, 128256, capi.FLAG_INPUT_READY), (148, 70001, capi.FLAG_INPUT_READY), (512, 256000, 0),
+                              (296, 9001, capi.FLAG_INPUT_READY), (592, 20000, 0)):
+        for dtype, esz in ((capi.F32, 4), (capi.BF16, 2)):
+            for k in (1, 50, 128):
+                for itype, isz in ((capi.I32, 4), (capi.I64, 8)):
+                    d = capi.SoftmaxTopkDesc(rows=rows, cols=cols, row_stride=cols, dtype=dtype, k=k, index_dtype=itype,
+                                             value_kind=0, inv_temperature=1.0, largest=1, path=capi.PATH_STREAM, splits=0,
+                                             index_offset=0, flags=flags, reserved=0)
+                    need = rows * 16 * (16 + up16(k * esz) + up16(k * isz)) + 2 * rows * 4
+                    assert capi.softmax_topk_workspace_bytes(d) >= need, (rows, cols, dtype, k, itype)
+
+
 def test_oracle_sampling_known_answers():
     v = np.array([[0.5, 0.3, 0.1, 0.05]], np.float32)
     ids = np.array([[7, 3, 9, 1]])
